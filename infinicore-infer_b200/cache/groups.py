@@ -45,13 +45,26 @@ class CacheNeed:
 
 @dataclass(frozen=True)
 class PagedKV(CacheNeed):
-    """Keys and values of ``num_kv_heads`` heads of ``head_dim`` for every cached position."""
+    """Keys and values of ``num_kv_heads`` heads of ``head_dim`` (values: ``v_head_dim`` if given) for every cached
+    position."""
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None      # None: all keys are kept
+    v_head_dim: Optional[int] = None  # None: as head_dim
 
     def group_key(self):
         return self
+
+    def shared_with(self, other) -> Optional["PagedKV"]:
+        """The need of a cache that one layer writes as ``self`` asks and another reads as ``other`` asks: the same pages
+        kept for the wider of the two windows.  None if the two cannot share (other sizes, another kind of need)."""
+        if not isinstance(other, PagedKV):
+            return None
+        if (self.num_kv_heads, self.head_dim, self.v_head_dim or self.head_dim) != \
+                (other.num_kv_heads, other.head_dim, other.v_head_dim or other.head_dim):
+            return None
+        window = None if self.window is None or other.window is None else max(self.window, other.window)
+        return PagedKV(self.num_kv_heads, self.head_dim, window, self.v_head_dim)
 
     def make_group(self, cache_ids, num_pages: int, page_size: int, max_blocks: int) -> "CacheGroup":
         return CacheGroup(self, cache_ids, num_pages, page_size, max_blocks=max_blocks)
@@ -61,8 +74,9 @@ class PagedKV(CacheNeed):
         if device is None:
             return None
         shape = (count, num_pages, self.num_kv_heads, page_size, self.head_dim)
+        v_shape = shape[:-1] + (self.v_head_dim or self.head_dim,)
         # zeros: what lies beyond a request's last position in a held page must be finite for every kernel
-        return torch.zeros(shape, dtype=dtype, device=device), torch.zeros(shape, dtype=dtype, device=device)
+        return torch.zeros(shape, dtype=dtype, device=device), torch.zeros(v_shape, dtype=dtype, device=device)
 
     def make_view(self, storage, index: int, group_index: int, page_size: int):
         from .manager import KVView
@@ -100,7 +114,8 @@ class CacheGroup:
         self.need = need
         self.cache_ids = list(cache_ids)
         self.page_size = page_size
-        self.name = name or f"kv{need.num_kv_heads}x{need.head_dim}" + (f"w{need.window}" if need.window else "")
+        self.name = name or f"kv{need.num_kv_heads}x{need.head_dim}" + (f"v{need.v_head_dim}" if need.v_head_dim else "") + \
+            (f"w{need.window}" if need.window else "")
         self.pool = PagePool(num_pages, reserved=1, name=self.name)
         self.tables: Dict[object, List[int]] = {}      # request -> page of each block (NO_PAGE if none)
         self.first_block: Dict[object, int] = {}       # request -> first block still held

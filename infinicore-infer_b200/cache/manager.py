@@ -36,8 +36,11 @@ class StateView:
 class CacheManager:
     def __init__(self, needs: Sequence[object], num_pages: int, page_size: int, max_requests: int,
                  max_positions: int, dtype: torch.dtype = torch.bfloat16, device=None,
-                 pages_per_group: Optional[Dict[int, int]] = None):
-        """``needs[c]`` is what cache ``c`` asks for: a ``PagedKV``, a ``StateSlot`` or None.
+                 pages_per_group: Optional[Dict[int, int]] = None, entry_states: Sequence[object] = ()):
+        """``needs[c]`` is what cache ``c`` asks for: a ``PagedKV``, a ``StateSlot`` or None.  ``entry_states[i]`` is the
+        state that entry i of the run order keeps for itself beside its cache (a ``StateSlot`` or None: the tail of a
+        short convolution, say, which a layer has even when the keys it reads are another layer's); its view is
+        ``state_views[i]``.
 
         ``num_pages`` is the number of usable pages of every group (one more, the null page,
         is added); ``pages_per_group`` overrides it by group index.
@@ -76,6 +79,14 @@ class CacheManager:
                 if storage is not None and hasattr(storage, "zero_"):
                     self._state_tensors.append(storage)
                 self.views[c] = need.make_view(storage, 0, -1, page_size)
+
+        self.state_views: List[object] = [None] * len(entry_states)
+        for i, need in enumerate(entry_states):
+            if need is not None:
+                storage = need.make_storage(1, 0, page_size, self.slots.num_slots, dtype, device)
+                if storage is not None and hasattr(storage, "zero_"):
+                    self._state_tensors.append(storage)
+                self.state_views[i] = need.make_view(storage, 0, -1, page_size)
 
     # ---- requests ------------------------------------------------------------------------
     def admit(self, req) -> int:

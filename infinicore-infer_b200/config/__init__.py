@@ -1,7 +1,8 @@
 """Configuration: typed specifications, the MiniCPM/FM9G config, the architecture registry."""
-from .specs import (AttentionSpec, BlockSpec, ConfigError, ModelSpec, RMSNormSpec, RopeSpec,
-                    RunEntry, SwiGLUSpec, default_order)
+from .specs import (AttentionSpec, BlockSpec, ConfigError, ConvAttentionSpec, GLUSpec, LayerNormSpec, LinearAttentionSpec,
+                    ModelSpec, PairRotarySpec, PostNormBlockSpec, RMSNormSpec, RopeSpec, RunEntry, SwiGLUSpec, default_order)
 from .minicpm import MiniCPMConfig
+from .sitelorn import SitelornConfig
 from .presets import PRESETS, Preset
 from .registry import (architecture_names, config_class_for, read_config,
                        register_architecture)
@@ -10,7 +11,10 @@ from .registry import (architecture_names, config_class_for, read_config,
 for _name in ("minicpm", "fm9g", "llama", "MiniCPMForCausalLM", "LlamaForCausalLM"):
     register_architecture(_name, MiniCPMConfig)
 
+register_architecture("sitelorn", SitelornConfig)
+
 __all__ = [
+    "ConvAttentionSpec", "GLUSpec", "LayerNormSpec", "LinearAttentionSpec", "PairRotarySpec", "PostNormBlockSpec", "SitelornConfig",
     "AttentionSpec", "BlockSpec", "ConfigError", "ModelSpec", "RMSNormSpec", "RopeSpec",
     "RunEntry", "SwiGLUSpec", "default_order", "MiniCPMConfig", "architecture_names",
     "config_class_for", "read_config", "register_architecture", "PRESETS", "Preset",

@@ -25,10 +25,11 @@ def architecture_names():
 
 
 def config_class_for(cfg: dict) -> type:
-    """Look the architecture up by ``model_type``, then by ``architectures``."""
+    """Look the architecture up by ``model_type``, then by ``architecture``, then by ``architectures``."""
     keys = []
-    if cfg.get("model_type"):
-        keys.append(str(cfg["model_type"]))
+    for single in ("model_type", "architecture"):
+        if cfg.get(single):
+            keys.append(str(cfg[single]))
     keys.extend(str(a) for a in cfg.get("architectures") or ())
     for k in keys:
         cls = _ARCHITECTURES.get(k.lower())
@@ -46,4 +47,9 @@ def read_config(model_dir: str, max_tokens: Optional[int] = None):
         raise ConfigError(f"no config.json in {model_dir}")
     with open(path) as f:
         cfg = json.load(f)
-    return config_class_for(cfg).from_dict(cfg, max_tokens=max_tokens)
+    cls = config_class_for(cfg)
+    if getattr(cls, "reads_shapes", False):       # a size that only a tensor's shape gives
+        from ..weights import index_directory
+        shapes = {name: tuple(info.shape) for name, info in index_directory(model_dir).items()}
+        return cls.from_dict(cfg, max_tokens=max_tokens, shapes=shapes)
+    return cls.from_dict(cfg, max_tokens=max_tokens)

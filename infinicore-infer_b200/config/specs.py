@@ -71,6 +71,121 @@ class SwiGLUSpec:
 
 
 @dataclass(frozen=True)
+class LayerNormSpec:
+    """y = (x - mean(x)) / sqrt(mean((x - mean(x))^2) + eps) * w + b, in float32.  ``weight_name`` and ``bias_name`` are
+    appended to the part's prefix."""
+    size: int
+    eps: float
+    weight_name: str = "weight"
+    bias_name: str = "bias"
+    kind: str = "layernorm"
+
+
+@dataclass(frozen=True)
+class PairRotarySpec:
+    """Rotation of the first ``dims`` elements of a head in pairs (2i, 2i+1) by the angle ``p * base ** (-2i / dims)``,
+    formed in float32 from the position; the other elements pass unchanged.  Needs no table and no longest position."""
+    dims: int
+    base: float
+    kind: str = "pair_rotary"
+
+
+@dataclass(frozen=True)
+class ConvAttentionSpec:
+    """Softmax attention over a paged cache with grouped heads whose keys and values may differ in size, and with these
+    options, each a parameter: a short causal convolution over time on every channel of the q, k and v projections
+    (``conv_taps`` taps, 0 for none), an RMS norm over the WHOLE q and the whole k projection (``qk_norm``), a rotation
+    (``position``), a sliding window, a sink (a key of score 0 without a value in every softmax), one output gate per
+    head (sigmoid of a projection of the mixer's input), and ``shares_kv``: the layer makes queries only and reads the
+    keys and values that another layer wrote into its cache.  The names are those of the checkpoint's tensors below the
+    mixer's prefix: projection ``q``, its convolution ``q`` + ``conv_suffix``, its norm ``q`` + ``norm_suffix``."""
+    hidden_size: int
+    num_heads: int
+    num_kv_heads: int
+    head_dim: int
+    v_head_dim: int
+    softmax_scale: float
+    window: Optional[int] = None
+    conv_taps: int = 0
+    qk_norm: bool = False
+    qk_norm_eps: float = 1e-6
+    position: Optional[PairRotarySpec] = None
+    sink: bool = False
+    head_gate: bool = False
+    shares_kv: bool = False
+    q_name: str = "q"
+    k_name: str = "k"
+    v_name: str = "v"
+    gate_name: str = "g"
+    o_name: str = "o"
+    conv_suffix: str = ".conv"
+    norm_suffix: str = ".norm"
+    kind: str = "conv_attention"
+
+
+@dataclass(frozen=True)
+class LinearAttentionSpec:
+    """Linear attention as a recurrence per head: S_t = diag(a_t) S_(t-1) + k_t v_t^T, o_t = S_t^T q_t, with the state
+    S [head_dim, v_head_dim] in float32 per request.
+
+    ``decay``: one constant per head (then a_t is that constant for every key channel), or None with ``decay_rank`` > 0:
+    a_t = sigmoid(W2 (W1 h) + b2) ** (1 / decay_tau), one value per key channel and token (W1: ``decay_down_name``,
+    [rank, hidden]; W2: ``decay_up_name`` [heads * head_dim, rank] with bias ``decay_up_name`` + ``bias_suffix``).
+    ``qkv_act`` acts on q, k and v ("none" or "silu"); q is multiplied by ``q_scale``.  The output passes an RMS norm,
+    over all heads at once with a weight of heads * v_head_dim (``norm_per_head`` False) or per head with one weight of
+    v_head_dim shared by the heads, is multiplied by ``gate_act`` of a projection of the mixer's input, and projected."""
+    hidden_size: int
+    num_heads: int
+    head_dim: int
+    v_head_dim: int
+    norm_eps: float
+    qkv_act: str = "none"
+    q_scale: float = 1.0
+    decay: Optional[Tuple[float, ...]] = None
+    decay_rank: int = 0
+    decay_tau: float = 1.0
+    norm_per_head: bool = False
+    gate_act: str = "sigmoid"
+    q_name: str = "q"
+    k_name: str = "k"
+    v_name: str = "v"
+    gate_name: str = "g"
+    o_name: str = "o"
+    norm_name: str = "norm"
+    decay_down_name: str = "a1"
+    decay_up_name: str = "a2"
+    bias_suffix: str = ".b"
+    kind: str = "linear_attention"
+
+
+@dataclass(frozen=True)
+class GLUSpec:
+    """down(act(gate(x)) * up(x)) with ``act`` "silu" or "gelu_tanh" (0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))))."""
+    hidden_size: int
+    intermediate_size: int
+    act: str = "gelu_tanh"
+    gate_name: str = "gate"
+    up_name: str = "up"
+    down_name: str = "down"
+    kind: str = "glu"
+
+
+@dataclass(frozen=True)
+class PostNormBlockSpec:
+    """One layer whose norms sit on the sublayers' outputs: x += norm_a(mixer(x)); x += norm_b(feed_forward(x)).  The
+    sublayers read the stream itself.  ``feed_forward`` None: the layer has a mixer only."""
+    mixer: object
+    feed_forward: Optional[object]
+    mixer_norm: object
+    ffn_norm: Optional[object]
+    mixer_prefix: str = "mix."
+    ffn_prefix: str = "mlp."
+    mixer_norm_prefix: str = "norm1"
+    ffn_norm_prefix: str = "norm2"
+    kind: str = "postnorm"
+
+
+@dataclass(frozen=True)
 class BlockSpec:
     """One layer: x += s * mixer(norm_a(x)); x += s * feed_forward(norm_b(x)).
 

@@ -28,6 +28,12 @@ struct AttnArgs {
     const int *block_table; // [nreq, max_blocks]
     int T, nh, nkvh, dh, page_size, max_blocks, window;
     float scale;
+    // what only the row kernel takes: values of another size than the keys (v_pages [pages, nkvh, page_size, dv], out
+    // [T, nh, dv]), a sink (a key of score 0 without a value: one more term, exp(0), in the normaliser), and a float32
+    // gate per row and head whose sigmoid multiplies the head's output (gate[t * gate_ld + h]; null: none)
+    int dv, sink;
+    const float *gate;
+    int gate_ld;
 };
 
 // ---------------------------------------------------------------------------------------
@@ -38,7 +44,7 @@ struct AttnArgs {
 constexpr int ROW_WARPS = 4;
 constexpr int ROW_MAX_DH = 512;
 
-template <typename T, int NS>     // NS: slices of 32 elements that cover one head
+template <typename T, int NS>     // NS: slices of 32 elements that cover one head's values
 __global__ void __launch_bounds__(ROW_WARPS * 32)
 attention_row_kernel(AttnArgs a) {
     pdl_trigger();
@@ -48,7 +54,7 @@ attention_row_kernel(AttnArgs a) {
     const int t = blockIdx.y;
     const int h = blockIdx.x * ROW_WARPS + warp;
     if (h >= a.nh) return;
-    const int dh = a.dh;
+    const int dh = a.dh, dv = a.dv;
     const int hk = h / (a.nh / a.nkvh);
     const int pos = a.positions[t];
     const int *bt = a.block_table + (size_t)a.row_req[t] * a.max_blocks;
@@ -61,8 +67,9 @@ attention_row_kernel(AttnArgs a) {
 
     const T *kp = (const T *)a.k_pages;
     const T *vp = (const T *)a.v_pages;
-    const size_t head_off = (size_t)hk * a.page_size * dh;
-    const size_t page_stride = (size_t)a.nkvh * a.page_size * dh;
+    // offsets are counted in rows of a key/value head: a key row has dh elements, a value row dv
+    const size_t head_off = (size_t)hk * a.page_size;
+    const size_t page_stride = (size_t)a.nkvh * a.page_size;
 
     float m = -INFINITY, l = 0.f;
     float acc[NS];
@@ -76,8 +83,8 @@ attention_row_kernel(AttnArgs a) {
         float s = -INFINITY;
         if (valid) {
             const int page = bt[j / a.page_size];
-            row_off = (size_t)page * page_stride + head_off + (size_t)(j % a.page_size) * dh;
-            const T *kr = kp + row_off;
+            row_off = (size_t)page * page_stride + head_off + (size_t)(j % a.page_size);
+            const T *kr = kp + row_off * dh;
             float dot = 0.f;
             for (int e = 0; e < dh; ++e) dot = fmaf(qs[e], to_f32(kr[e]), dot);
             s = dot * a.scale;
@@ -93,20 +100,28 @@ attention_row_kernel(AttnArgs a) {
         for (int jj = 0; jj < n; ++jj) {
             const float pj = __shfl_sync(0xffffffffu, p, jj);
             const unsigned long long off = __shfl_sync(0xffffffffu, (unsigned long long)row_off, jj);
-            const T *vr = vp + off;
+            const T *vr = vp + off * dv;
 #pragma unroll
             for (int i = 0; i < NS; ++i) {
                 const int e = lane + 32 * i;
-                if (e < dh) acc[i] = fmaf(pj, to_f32(vr[e]), acc[i]);
+                if (e < dv) acc[i] = fmaf(pj, to_f32(vr[e]), acc[i]);
             }
         }
     }
-    T *orow = (T *)a.out + ((size_t)t * a.nh + h) * dh;
-    const float inv = 1.f / l;
+    if (a.sink) {       // one more key of score 0 that brings no value
+        const float m_new = fmaxf(m, 0.f);
+        const float corr = expf(m - m_new);
+        l = l * corr + expf(-m_new);
+#pragma unroll
+        for (int i = 0; i < NS; ++i) acc[i] *= corr;
+    }
+    T *orow = (T *)a.out + ((size_t)t * a.nh + h) * dv;
+    float inv = 1.f / l;
+    if (a.gate != nullptr) inv *= 1.f / (1.f + expf(-a.gate[(size_t)t * a.gate_ld + h]));
 #pragma unroll
     for (int i = 0; i < NS; ++i) {
         const int e = lane + 32 * i;
-        if (e < dh) orow[e] = from_f32<T>(acc[i] * inv);
+        if (e < dv) orow[e] = from_f32<T>(acc[i] * inv);
     }
 }
 
@@ -122,22 +137,25 @@ static int check_args(const AttnArgs &a) {
 JK_EXPORT int jk_attention_rows(const void *q, const void *k_pages, const void *v_pages, void *out,
                                 int dtype, const int *positions, const int *row_req,
                                 const int *block_table, int max_blocks, int page_size, int T, int nh,
-                                int nkvh, int dh, float scale, int window, cudaStream_t stream) {
+                                int nkvh, int dh, float scale, int window, int dv, int sink, const float *gate, int gate_ld,
+                                cudaStream_t stream) {
     if (T == 0) return JK_OK;
+    if (dv <= 0) dv = dh;
     AttnArgs a{q, k_pages, v_pages, out, positions, row_req, block_table,
-               T, nh, nkvh, dh, page_size, max_blocks, window, scale};
+               T, nh, nkvh, dh, page_size, max_blocks, window, scale, dv, sink, gate, gate_ld};
     if (int rc = check_args(a)) return rc;
-    JK_REQUIRE(dh <= ROW_MAX_DH, "attention: head size %d exceeds %d", dh, ROW_MAX_DH);
+    JK_REQUIRE(dh <= ROW_MAX_DH && dv <= ROW_MAX_DH, "attention: head size %d / %d exceeds %d", dh, dv, ROW_MAX_DH);
+    JK_REQUIRE(gate == nullptr || gate_ld >= nh, "attention: a gate row of %d holds no %d heads", gate_ld, nh);
     JK_REQUIRE(T <= 65535, "attention: %d rows exceed one launch (65535)", T);
     dim3 grid((nh + ROW_WARPS - 1) / ROW_WARPS, T);
     const size_t smem = (size_t)ROW_WARPS * dh * sizeof(float);
 #define LAUNCH_ROWS(T, NS) jk_launch(attention_row_kernel<T, NS>, grid, dim3(ROW_WARPS * 32), smem, stream, a)
 #define LAUNCH_ROWS_T(T)                                \
     do {                                                \
-        if (dh <= 32) LAUNCH_ROWS(T, 1);                \
-        else if (dh <= 64) LAUNCH_ROWS(T, 2);           \
-        else if (dh <= 128) LAUNCH_ROWS(T, 4);          \
-        else if (dh <= 256) LAUNCH_ROWS(T, 8);          \
+        if (dv <= 32) LAUNCH_ROWS(T, 1);                \
+        else if (dv <= 64) LAUNCH_ROWS(T, 2);           \
+        else if (dv <= 128) LAUNCH_ROWS(T, 4);          \
+        else if (dv <= 256) LAUNCH_ROWS(T, 8);          \
         else LAUNCH_ROWS(T, 16);                        \
     } while (0)
     if (dtype == JK_F32)

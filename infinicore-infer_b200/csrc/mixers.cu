@@ -1,0 +1,513 @@
+// Kernels of mixers and norms beyond the softmax-attention decoder: layer norm (on a sublayer's output, added into the
+// stream; or of chosen rows), gated feed-forward activations, short causal convolutions over time with their per-request
+// tails, whole-projection RMS norm and partial interleaved rotation of queries and keys, linear-attention recurrences
+// with a constant or a projected decay, and the norm + gate that follows them.
+//
+// Everything a recurrence touches is float32: the state, the decays and their logarithms, the gates, the norms.  The
+// projections arrive as float32 rows of one fused product ([q | k | v | gate | ...] side by side, `ld` apart); what the
+// next product reads is written in the activation type T (float or bfloat16), rounded once.
+//
+// A step's rows are laid out request after request: request i owns rows req_start[i] .. req_start[i+1]-1, which continue
+// the sequence at position req_pos[i]; its state lives in slot slot_ids[i] of each state tensor.  A kernel that carries
+// state reads what earlier steps left and leaves what later steps need, so a whole prompt, a portion and a single token
+// are one case.
+#include "common.cuh"
+
+#include <algorithm>
+
+JK_DEFINE_ERROR_BUFFER(jk_mixers)
+
+// accurate forms: no fast-math anywhere in this package
+__device__ __forceinline__ float sigmoid_f(float z) { return 1.f / (1.f + expf(-z)); }
+__device__ __forceinline__ float silu_f(float z) { return z / (1.f + expf(-z)); }
+__device__ __forceinline__ float gelu_tanh_f(float z) {
+    return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+// log(sigmoid(z)) without overflow on either side
+__device__ __forceinline__ float log_sigmoid_f(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
+
+enum MixAct : int { ACT_NONE = 0, ACT_SILU = 1, ACT_GELU_TANH = 2, ACT_SIGMOID = 3 };
+__device__ __forceinline__ float apply_act(int act, float z) {
+    switch (act) {
+        case ACT_SILU: return silu_f(z);
+        case ACT_GELU_TANH: return gelu_tanh_f(z);
+        case ACT_SIGMOID: return sigmoid_f(z);
+        default: return z;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Layer norm: y = (v - mean(v)) / sqrt(mean((v - mean)^2) + eps) * w + b, one block per row, the row held in shared
+// memory between the passes (mean first, then the mean of the squared deviations).
+//   add mode   (x_add != null): v = delta[r]; x[r] += y; h[r] = T(x[r]) if h is given      (norm on a sublayer's output)
+//   rows mode  (x_add == null): v = x[rows ? rows[i] : i]; out[i] = T(y)                     (a norm that feeds a product)
+// ---------------------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void layernorm_kernel(const float *__restrict__ src, const int *__restrict__ rows, const float *__restrict__ w,
+                                 const float *__restrict__ b, float eps, float *__restrict__ x_add, T *__restrict__ out, int d) {
+    pdl_trigger();
+    pdl_wait();
+    extern __shared__ __align__(16) float row_buf[];
+    __shared__ float scratch[33];
+    const int i = blockIdx.x;
+    const int r = rows ? rows[i] : i;
+    const float *v = src + (size_t)r * d;
+    float s = 0.f;
+    for (int c = threadIdx.x; c < d; c += blockDim.x) {
+        const float t = v[c];
+        row_buf[c] = t;
+        s += t;
+    }
+    const float mean = block_sum(s, scratch) / (float)d;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < d; c += blockDim.x) {
+        const float t = row_buf[c] - mean;
+        ss += t * t;
+    }
+    const float inv = 1.f / sqrtf(block_sum(ss, scratch) / (float)d + eps);
+    for (int c = threadIdx.x; c < d; c += blockDim.x) {
+        const float y = (row_buf[c] - mean) * inv * w[c] + (b ? b[c] : 0.f);
+        if (x_add != nullptr) {
+            const float nx = x_add[(size_t)r * d + c] + y;
+            x_add[(size_t)r * d + c] = nx;
+            if (out != nullptr) out[(size_t)i * d + c] = from_f32<T>(nx);
+        } else {
+            out[(size_t)i * d + c] = from_f32<T>(y);
+        }
+    }
+}
+
+// add mode: x [nrows, d] += LN(delta [nrows, d]); h (type `dtype`, may be null) = x.   rows mode: out = LN(x[rows]).
+JK_EXPORT int jk_layernorm(const float *src, const int *rows, int nrows, int d, const float *w, const float *b, float eps,
+                           float *x_add, void *out, int dtype, cudaStream_t stream) {
+    if (nrows == 0) return JK_OK;
+    JK_REQUIRE(src && w && nrows > 0 && d > 0, "layernorm: rows %d, width %d", nrows, d);
+    JK_REQUIRE(x_add != nullptr || out != nullptr, "layernorm: nothing to write");
+    JK_REQUIRE(x_add == nullptr || rows == nullptr, "layernorm: the adding form works on every row");
+    JK_REQUIRE((size_t)d * 4 <= 200 * 1024, "layernorm: width %d does not fit shared memory", d);
+    const int threads = d >= 2048 ? 512 : (d >= 512 ? 256 : 128);
+    const size_t smem = (size_t)d * sizeof(float);
+    if (dtype == JK_F32) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(layernorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        jk_launch(layernorm_kernel<float>, dim3(nrows), dim3(threads), smem, stream, src, rows, w, b, eps, x_add, (float *)out, d);
+    } else if (dtype == JK_BF16) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(layernorm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        jk_launch(layernorm_kernel<__nv_bfloat16>, dim3(nrows), dim3(threads), smem, stream, src, rows, w, b, eps, x_add,
+                  (__nv_bfloat16 *)out, d);
+    } else {
+        JK_FAIL(JK_UNSUPPORTED, "layernorm: dtype %d", dtype);
+    }
+    JK_CHECK_LAUNCH("layernorm");
+    return JK_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// out = T(in): the float32 stream as the operand of a product that reads the stream itself.
+// ---------------------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void cast_kernel(const float *__restrict__ in, T *__restrict__ out, size_t n) {
+    pdl_trigger();
+    pdl_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) out[i] = from_f32<T>(in[i]);
+}
+
+JK_EXPORT int jk_cast_rows(const float *in, void *out, int dtype, long long n, cudaStream_t stream) {
+    if (n == 0) return JK_OK;
+    JK_REQUIRE(in && out && n > 0, "cast: nothing to do it with");
+    const int blocks = (int)std::min<long long>((n + 255) / 256, 148 * 16);
+    if (dtype == JK_F32)
+        jk_launch(cast_kernel<float>, dim3(blocks), dim3(256), 0, stream, in, (float *)out, (size_t)n);
+    else if (dtype == JK_BF16)
+        jk_launch(cast_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, in, (__nv_bfloat16 *)out, (size_t)n);
+    else
+        JK_FAIL(JK_UNSUPPORTED, "cast: dtype %d", dtype);
+    JK_CHECK_LAUNCH("cast");
+    return JK_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Gated linear unit: out[t, c] = act(gu[t, c]) * gu[t, di + c], gu float32 [T, 2 di].
+// ---------------------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void glu_kernel(const float *__restrict__ gu, T *__restrict__ out, int di, size_t total, int act) {
+    pdl_trigger();
+    pdl_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = i / di, c = i % di;
+        const float g = gu[t * 2 * di + c], u = gu[t * 2 * di + di + c];
+        out[i] = from_f32<T>(apply_act(act, g) * u);
+    }
+}
+
+JK_EXPORT int jk_glu(const float *gu, void *out, int dtype, int ntok, int di, int act, cudaStream_t stream) {
+    if (ntok == 0) return JK_OK;
+    JK_REQUIRE(gu && out && ntok > 0 && di > 0, "glu: rows %d, width %d", ntok, di);
+    const size_t total = (size_t)ntok * di;
+    const int blocks = (int)std::min<size_t>((total + 255) / 256, 148 * 16);
+    if (dtype == JK_F32)
+        jk_launch(glu_kernel<float>, dim3(blocks), dim3(256), 0, stream, gu, (float *)out, di, total, act);
+    else if (dtype == JK_BF16)
+        jk_launch(glu_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, gu, (__nv_bfloat16 *)out, di, total, act);
+    else
+        JK_FAIL(JK_UNSUPPORTED, "glu: dtype %d", dtype);
+    JK_CHECK_LAUNCH("glu");
+    return JK_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Queries, keys and values of a softmax attention whose projections pass a short causal convolution over time, an RMS
+// norm over the whole projection (queries and keys) and a rotation of the first `rot_dims` elements of each head:
+//     y_t[c]  = sum_j conv[c, j] * u_(t - taps + 1 + j)[c]         u: the projection; zeros before the sequence starts
+//     q_t     = rotate(y_t * norm_w / sqrt(mean(y_t^2) + eps))     the mean over all heads' elements at once
+//     rotate: (a, b) = elements (2i, 2i+1) of a head, i < rot_dims / 2, at position p:
+//             (a cos(p f_i) - b sin(p f_i), b cos(p f_i) + a sin(p f_i)),  the angle p * f_i formed in float32
+// The projections before a portion's first row come from the request's tail: the last taps - 1 projected rows of its
+// sequence, tail[slot, s, c], s = taps - 2 the newest.  One block per row.  Queries go to q_out [T, nq]; keys (after
+// everything) and values (after the convolution) into their pages at the row's position.  `conv_tail_kernel` then
+// moves the tails forward; it runs after this kernel has read them.
+// ---------------------------------------------------------------------------------------------------------------
+struct ConvQkvArgs {
+    const float *u;             // [T, ld]
+    int ld, q_off, k_off, v_off;
+    int nq, nk, nv;             // channels: heads * dk, kv_heads * dk, kv_heads * dv; nk = nv = 0: queries only
+    const float *conv_q, *conv_k, *conv_v;      // [channels, taps]; null: no convolution
+    const float *norm_q, *norm_k;               // [nq], [nk]; null: no norm
+    const float *freq;          // [rot_dims / 2] float32: f_i
+    float *tail;                // [slots, taps - 1, nq + nk + nv]
+    int taps, dk, dv, kv_heads, rot_dims;
+    float eps;
+    const int *positions, *row_req, *req_start, *slot_ids, *block_table;
+    int max_blocks, page_size;
+    void *q_out, *k_pages, *v_pages;
+};
+
+template <typename T>
+__global__ void conv_qkv_kernel(ConvQkvArgs a) {
+    pdl_trigger();
+    pdl_wait();
+    extern __shared__ __align__(16) float y[];      // [nq + nk + nv]
+    __shared__ float scratch[33];
+    const int t = blockIdx.x;
+    const int C = a.nq + a.nk + a.nv;
+    const int req = a.row_req[t];
+    const int back = t - a.req_start[req];          // rows of this portion before this one
+    const int pos = a.positions[t];
+    const float *tail = a.tail ? a.tail + (size_t)a.slot_ids[req] * (a.taps - 1) * C : nullptr;
+    float ssq = 0.f, ssk = 0.f;
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+        int col;
+        const float *w;
+        if (c < a.nq) { col = a.q_off + c; w = a.conv_q ? a.conv_q + (size_t)c * a.taps : nullptr; }
+        else if (c < a.nq + a.nk) { col = a.k_off + c - a.nq; w = a.conv_k ? a.conv_k + (size_t)(c - a.nq) * a.taps : nullptr; }
+        else { col = a.v_off + c - a.nq - a.nk; w = a.conv_v ? a.conv_v + (size_t)(c - a.nq - a.nk) * a.taps : nullptr; }
+        float acc;
+        if (w == nullptr) {
+            acc = a.u[(size_t)t * a.ld + col];
+        } else {
+            acc = 0.f;
+            for (int j = 0; j < a.taps; ++j) {
+                const int d = a.taps - 1 - j;       // how many rows back
+                float uv;
+                if (d <= back) uv = a.u[(size_t)(t - d) * a.ld + col];
+                else uv = tail[(size_t)(a.taps - 1 + back - d) * C + c];
+                acc = fmaf(w[j], uv, acc);
+            }
+        }
+        y[c] = acc;
+        if (c < a.nq) ssq += acc * acc;
+        else if (c < a.nq + a.nk) ssk += acc * acc;
+    }
+    const float sum_q = block_sum(ssq, scratch);
+    const float sum_k = a.nk > 0 ? block_sum(ssk, scratch) : 0.f;
+    const float inv_q = a.norm_q ? 1.f / sqrtf(sum_q / (float)a.nq + a.eps) : 1.f;
+    const float inv_k = (a.norm_k && a.nk > 0) ? 1.f / sqrtf(sum_k / (float)a.nk + a.eps) : 1.f;
+    for (int c = threadIdx.x; c < a.nq + a.nk; c += blockDim.x) {
+        const bool is_q = c < a.nq;
+        const int cc = is_q ? c : c - a.nq;
+        const float *nw = is_q ? a.norm_q : a.norm_k;
+        y[c] = y[c] * (is_q ? inv_q : inv_k) * (nw ? nw[cc] : 1.f);
+    }
+    __syncthreads();
+    // rotation and the stores; a thread reads its partner's element, nobody writes y any more
+    T *q_out = (T *)a.q_out + (size_t)t * a.nq;
+    const float fpos = (float)pos;
+    size_t k_row = 0, v_row = 0;
+    if (a.nk > 0) {
+        const int page = a.block_table[(size_t)req * a.max_blocks + pos / a.page_size];
+        const size_t row = (size_t)page * a.kv_heads * a.page_size + (size_t)(pos % a.page_size);
+        k_row = row; v_row = row;
+    }
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+        if (c < a.nq + a.nk) {
+            const bool is_q = c < a.nq;
+            const int cc = is_q ? c : c - a.nq;
+            const int head = cc / a.dk, e = cc % a.dk;
+            float val = y[c];
+            if (e < a.rot_dims) {
+                const float ang = fpos * a.freq[e >> 1];
+                float sn, cs;
+                sincosf(ang, &sn, &cs);
+                const float other = y[(e & 1) ? c - 1 : c + 1];
+                val = (e & 1) ? fmaf(val, cs, other * sn) : fmaf(val, cs, -other * sn);
+            }
+            if (is_q) q_out[cc] = from_f32<T>(val);
+            else ((T *)a.k_pages)[(k_row + (size_t)head * a.page_size) * a.dk + e] = from_f32<T>(val);
+        } else {
+            const int cc = c - a.nq - a.nk;
+            const int head = cc / a.dv, e = cc % a.dv;
+            ((T *)a.v_pages)[(v_row + (size_t)head * a.page_size) * a.dv + e] = from_f32<T>(y[c]);
+        }
+    }
+}
+
+// tail[slot, s, c] <- the projection taps - 1 - s rows before the end of the request's sequence after this step.
+// One thread per (request, channel); it reads every old entry it needs before it overwrites it (ascending s reads
+// ahead of the writes).
+__global__ void conv_tail_kernel(ConvQkvArgs a, int nreq) {
+    pdl_trigger();
+    pdl_wait();
+    const int C = a.nq + a.nk + a.nv;
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= nreq * C) return;
+    const int req = idx / C, c = idx % C;
+    const int first = a.req_start[req], n = a.req_start[req + 1] - first;
+    int col;
+    if (c < a.nq) col = a.q_off + c;
+    else if (c < a.nq + a.nk) col = a.k_off + c - a.nq;
+    else col = a.v_off + c - a.nq - a.nk;
+    float *tail = a.tail + (size_t)a.slot_ids[req] * (a.taps - 1) * C;
+    for (int s = 0; s < a.taps - 1; ++s) {
+        const int off = n - (a.taps - 1) + s;       // row of this portion (negative: before it)
+        const float v = off >= 0 ? a.u[(size_t)(first + off) * a.ld + col] : tail[(size_t)(s + n) * C + c];
+        tail[(size_t)s * C + c] = v;
+    }
+}
+
+JK_EXPORT int jk_conv_qkv(const float *u, int ld, int q_off, int k_off, int v_off, int heads, int kv_heads, int dk, int dv,
+                          int has_kv, const float *conv_q, const float *conv_k, const float *conv_v, int taps,
+                          const float *norm_q, const float *norm_k, float eps, const float *freq, int rot_dims, float *tail,
+                          const int *positions, const int *row_req, const int *req_start, const int *slot_ids,
+                          const int *block_table, int max_blocks, int page_size, void *q_out, void *k_pages, void *v_pages,
+                          int dtype, int T, int nreq, cudaStream_t stream) {
+    if (T == 0) return JK_OK;
+    ConvQkvArgs a;
+    a.u = u; a.ld = ld; a.q_off = q_off; a.k_off = k_off; a.v_off = v_off;
+    a.nq = heads * dk; a.nk = has_kv ? kv_heads * dk : 0; a.nv = has_kv ? kv_heads * dv : 0;
+    a.conv_q = conv_q; a.conv_k = conv_k; a.conv_v = conv_v; a.norm_q = norm_q; a.norm_k = norm_k; a.freq = freq; a.tail = tail;
+    a.taps = taps; a.dk = dk; a.dv = dv; a.kv_heads = kv_heads; a.rot_dims = rot_dims; a.eps = eps;
+    a.positions = positions; a.row_req = row_req; a.req_start = req_start; a.slot_ids = slot_ids; a.block_table = block_table;
+    a.max_blocks = max_blocks; a.page_size = page_size; a.q_out = q_out; a.k_pages = k_pages; a.v_pages = v_pages;
+    const bool conv = conv_q || conv_k || conv_v;
+    JK_REQUIRE(u && q_out && positions && row_req && req_start && heads > 0 && dk > 0, "conv_qkv: an argument is missing");
+    JK_REQUIRE(!has_kv || (k_pages && v_pages && block_table && kv_heads > 0 && dv > 0 && page_size > 0), "conv_qkv: keys without a cache");
+    JK_REQUIRE(!conv || (taps >= 1 && (taps == 1 || (tail && slot_ids))), "conv_qkv: a convolution of %d taps without its tails", taps);
+    JK_REQUIRE(rot_dims >= 0 && rot_dims <= dk && rot_dims % 2 == 0 && (rot_dims == 0 || freq), "conv_qkv: rotation of %d of %d elements", rot_dims, dk);
+    const int C = a.nq + a.nk + a.nv;
+    const size_t smem = (size_t)C * sizeof(float);
+    JK_REQUIRE(smem <= 200 * 1024, "conv_qkv: %d channels do not fit shared memory", C);
+    const int threads = C >= 2048 ? 512 : (C >= 512 ? 256 : 128);
+    if (dtype == JK_F32) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(conv_qkv_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        jk_launch(conv_qkv_kernel<float>, dim3(T), dim3(threads), smem, stream, a);
+    } else if (dtype == JK_BF16) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(conv_qkv_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        jk_launch(conv_qkv_kernel<__nv_bfloat16>, dim3(T), dim3(threads), smem, stream, a);
+    } else {
+        JK_FAIL(JK_UNSUPPORTED, "conv_qkv: dtype %d", dtype);
+    }
+    JK_CHECK_LAUNCH("conv_qkv");
+    if (conv && taps > 1) {
+        const int total = nreq * C;
+        jk_launch(conv_tail_kernel, dim3((total + 127) / 128), dim3(128), 0, stream, a, nreq);
+        JK_CHECK_LAUNCH("conv_tail");
+    }
+    return JK_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Linear attention as a recurrence over a request's rows, per head:
+//     S_t = diag(a_t) S_(t-1) + k_t v_t^T        S: [dk, dv] float32, carried in state[slot, head]
+//     o_t = S_t^T q_t
+// q, k, v pass `qkv_act` (none or silu); q is multiplied by q_scale.  The decay a_t [dk] is either one constant per head
+// (decay[head], for all channels and rows) or projected: z = W2 r_t + b2 with r_t the `rank` columns of the fused
+// product at r_off, a = exp(log_sigmoid(z) / tau), all in float32 (W2 may be stored as bfloat16).
+// A block owns (head, request, a slice of `cols` value columns) and walks the request's rows in order; its threads are
+// (key group, column): thread (g, v) keeps S[g-th slice of dk][v] in registers.  Rows of a step beyond one per request
+// cost a barrier each; the state is read and written once per step.
+// ---------------------------------------------------------------------------------------------------------------
+struct ScanArgs {
+    const float *u;             // [T, ld]
+    int ld, q_off, k_off, v_off, r_off;
+    int heads, dk, dv, qkv_act;
+    float q_scale;
+    const float *decay;         // [heads] or null
+    const void *w2;             // [heads * dk, rank] (W2T: float or bfloat16) or null
+    const float *b2;            // [heads * dk] or null
+    int rank;
+    float inv_tau;
+    float *state;               // [slots, heads, dk, dv]
+    const int *req_start, *slot_ids;
+    float *out;                 // [T, heads * dv] float32
+    int cols;                   // value columns per block
+};
+
+constexpr int SCAN_THREADS = 128;
+
+template <typename TW, int KS>      // KS: key channels per thread
+__global__ void __launch_bounds__(SCAN_THREADS)
+linear_scan_kernel(ScanArgs a) {
+    pdl_trigger();
+    pdl_wait();
+    extern __shared__ __align__(16) float sm[];
+    const int head = blockIdx.x, req = blockIdx.y, c0 = blockIdx.z * a.cols;
+    const int cols = min(a.cols, a.dv - c0);
+    const int groups = SCAN_THREADS / a.cols;           // key groups: groups * KS >= dk
+    float *sq = sm;                                     // [dk]
+    float *sk = sq + a.dk;                              // [dk]
+    float *sa = sk + a.dk;                              // [dk]
+    float *sv = sa + a.dk;                              // [cols]
+    float *part = sv + a.cols;                          // [groups, cols]
+    const int g = threadIdx.x / a.cols, v = threadIdx.x % a.cols;
+    const bool owner = g < groups && v < cols;
+    const int k0 = g * KS;
+    const int first = a.req_start[req], last = a.req_start[req + 1];
+    float *S = a.state + (((size_t)a.slot_ids[req] * a.heads + head) * a.dk) * a.dv + c0;
+    float s[KS];
+#pragma unroll
+    for (int i = 0; i < KS; ++i) s[i] = (owner && k0 + i < a.dk) ? S[(size_t)(k0 + i) * a.dv + v] : 0.f;
+    const float head_decay = a.decay ? a.decay[head] : 1.f;
+    for (int t = first; t < last; ++t) {
+        const float *row = a.u + (size_t)t * a.ld;
+        __syncthreads();            // the row before is done with sq / sk / sa / sv / part
+        for (int i = threadIdx.x; i < a.dk; i += SCAN_THREADS) {
+            sq[i] = apply_act(a.qkv_act, row[a.q_off + head * a.dk + i]) * a.q_scale;
+            sk[i] = apply_act(a.qkv_act, row[a.k_off + head * a.dk + i]);
+            float dec = head_decay;
+            if (a.w2 != nullptr) {
+                const TW *w = (const TW *)a.w2 + (size_t)(head * a.dk + i) * a.rank;
+                float z = a.b2 ? a.b2[head * a.dk + i] : 0.f;
+                for (int r = 0; r < a.rank; ++r) z = fmaf(to_f32(w[r]), row[a.r_off + r], z);
+                dec = expf(log_sigmoid_f(z) * a.inv_tau);
+            }
+            sa[i] = dec;
+        }
+        for (int i = threadIdx.x; i < cols; i += SCAN_THREADS) sv[i] = apply_act(a.qkv_act, row[a.v_off + head * a.dv + c0 + i]);
+        __syncthreads();
+        float o = 0.f;
+        if (owner) {
+            const float vv = sv[v];
+#pragma unroll
+            for (int i = 0; i < KS; ++i) {
+                if (k0 + i < a.dk) {
+                    s[i] = fmaf(sa[k0 + i], s[i], sk[k0 + i] * vv);
+                    o = fmaf(s[i], sq[k0 + i], o);
+                }
+            }
+            part[g * a.cols + v] = o;
+        }
+        __syncthreads();
+        if (threadIdx.x < cols) {
+            float sum = 0.f;
+            for (int gg = 0; gg < groups; ++gg) sum += part[gg * a.cols + threadIdx.x];
+            a.out[(size_t)t * a.heads * a.dv + head * a.dv + c0 + threadIdx.x] = sum;
+        }
+    }
+    if (owner) {
+#pragma unroll
+        for (int i = 0; i < KS; ++i)
+            if (k0 + i < a.dk) S[(size_t)(k0 + i) * a.dv + v] = s[i];
+    }
+}
+
+JK_EXPORT int jk_linear_scan(const float *u, int ld, int q_off, int k_off, int v_off, int heads, int dk, int dv, int qkv_act,
+                             float q_scale, const float *decay, const void *w2, int w2_dtype, const float *b2, int r_off, int rank,
+                             float tau, float *state, const int *req_start, const int *slot_ids, int nreq, int T, float *out,
+                             int sms, cudaStream_t stream) {
+    if (T == 0 || nreq == 0) return JK_OK;
+    JK_REQUIRE(u && state && req_start && slot_ids && out && heads > 0 && dk > 0 && dv > 0, "linear_scan: an argument is missing");
+    JK_REQUIRE((decay != nullptr) != (w2 != nullptr), "linear_scan: the decay is a constant per head or projected, one of the two");
+    JK_REQUIRE(w2 == nullptr || (rank > 0 && tau > 0.f), "linear_scan: a projected decay of rank %d, tau %g", rank, tau);
+    JK_REQUIRE(dk <= 1024, "linear_scan: %d key channels a head exceed 1024", dk);
+    // columns per block: a power of two up to 128; fewer columns make more blocks (a decode step of few requests should
+    // still reach every SM) and more key groups a block, as long as a thread keeps at most 64 channels
+    int cols = 1;
+    while (cols < dv && cols < SCAN_THREADS) cols *= 2;
+    const int sm_count = sms > 0 ? sms : 148;
+    while (cols > 8 && (long long)heads * nreq * ((dv + cols - 1) / cols) < 2LL * sm_count) cols /= 2;
+    while ((dk + SCAN_THREADS / cols - 1) / (SCAN_THREADS / cols) > 64) cols /= 2;
+    JK_REQUIRE(cols >= 1, "linear_scan: no way to cut %d x %d", dk, dv);
+    const int groups = SCAN_THREADS / cols;
+    const int per_thread = (dk + groups - 1) / groups;
+    ScanArgs a{u, ld, q_off, k_off, v_off, r_off, heads, dk, dv, qkv_act, q_scale, decay, w2, b2, rank, tau > 0.f ? 1.f / tau : 0.f,
+               state, req_start, slot_ids, out, cols};
+    dim3 grid(heads, nreq, (dv + cols - 1) / cols);
+    JK_REQUIRE(nreq <= 65535 && grid.z <= 65535, "linear_scan: %d requests in one launch", nreq);
+    const size_t smem = sizeof(float) * (3 * (size_t)dk + cols + (size_t)groups * cols);
+#define SCAN_LAUNCH(TW, KS) jk_launch(linear_scan_kernel<TW, KS>, grid, dim3(SCAN_THREADS), smem, stream, a)
+#define SCAN_LAUNCH_T(TW)                                   \
+    do {                                                    \
+        if (per_thread <= 1) SCAN_LAUNCH(TW, 1);            \
+        else if (per_thread <= 2) SCAN_LAUNCH(TW, 2);       \
+        else if (per_thread <= 4) SCAN_LAUNCH(TW, 4);       \
+        else if (per_thread <= 8) SCAN_LAUNCH(TW, 8);       \
+        else if (per_thread <= 16) SCAN_LAUNCH(TW, 16);     \
+        else if (per_thread <= 32) SCAN_LAUNCH(TW, 32);     \
+        else SCAN_LAUNCH(TW, 64);                           \
+    } while (0)
+    if (w2 != nullptr && w2_dtype == JK_BF16)
+        SCAN_LAUNCH_T(__nv_bfloat16);
+    else
+        SCAN_LAUNCH_T(float);
+    JK_CHECK_LAUNCH("linear_scan");
+    return JK_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// What follows a linear attention: RMS norm of its output (over all heads' values at once with a weight of that size,
+// or head by head with one weight of dv shared by the heads), times act(gate), into the activation type.
+//     out[t, c] = o[t, c] / sqrt(mean_scope(o^2) + eps) * w[c or c % dv] * act(u[t, g_off + c])
+// One block per row; a warp per head in the per-head form.
+// ---------------------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void norm_gate_kernel(const float *__restrict__ o, const float *__restrict__ u, int ld, int g_off, const float *__restrict__ w,
+                                 float eps, int heads, int dv, int per_head, int gate_act, T *__restrict__ out) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ float scratch[33];
+    const int t = blockIdx.x, n = heads * dv;
+    const float *orow = o + (size_t)t * n;
+    const float *grow = u + (size_t)t * ld + g_off;
+    T *dst = out + (size_t)t * n;
+    if (per_head) {
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+        for (int h = warp; h < heads; h += nwarp) {
+            float ss = 0.f;
+            for (int e = lane; e < dv; e += 32) { const float x = orow[h * dv + e]; ss += x * x; }
+            const float inv = 1.f / sqrtf(warp_sum(ss) / (float)dv + eps);
+            for (int e = lane; e < dv; e += 32)
+                dst[h * dv + e] = from_f32<T>(orow[h * dv + e] * inv * w[e] * apply_act(gate_act, grow[h * dv + e]));
+        }
+    } else {
+        float ss = 0.f;
+        for (int c = threadIdx.x; c < n; c += blockDim.x) { const float x = orow[c]; ss += x * x; }
+        const float inv = 1.f / sqrtf(block_sum(ss, scratch) / (float)n + eps);
+        for (int c = threadIdx.x; c < n; c += blockDim.x) dst[c] = from_f32<T>(orow[c] * inv * w[c] * apply_act(gate_act, grow[c]));
+    }
+}
+
+JK_EXPORT int jk_norm_gate(const float *o, const float *u, int ld, int g_off, const float *w, float eps, int heads, int dv,
+                           int per_head, int gate_act, void *out, int dtype, int T, cudaStream_t stream) {
+    if (T == 0) return JK_OK;
+    JK_REQUIRE(o && u && w && out && heads > 0 && dv > 0, "norm_gate: an argument is missing");
+    const int n = heads * dv;
+    const int threads = n >= 2048 ? 512 : (n >= 512 ? 256 : 128);
+    if (dtype == JK_F32)
+        jk_launch(norm_gate_kernel<float>, dim3(T), dim3(threads), 0, stream, o, u, ld, g_off, w, eps, heads, dv, per_head, gate_act, (float *)out);
+    else if (dtype == JK_BF16)
+        jk_launch(norm_gate_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, o, u, ld, g_off, w, eps, heads, dv, per_head, gate_act,
+                  (__nv_bfloat16 *)out);
+    else
+        JK_FAIL(JK_UNSUPPORTED, "norm_gate: dtype %d", dtype);
+    JK_CHECK_LAUNCH("norm_gate");
+    return JK_OK;
+}

@@ -51,6 +51,10 @@ JK_EXPORT int jk_runner_bind(const RunnerFns *fns) {
                (f.gemm_tcgen05 != nullptr) == (f.err_gemm_tcgen05 != nullptr) &&
                (f.attention_tcgen05 != nullptr) == (f.err_attention_tcgen05 != nullptr),
                "runner_bind: a module's entries come together");
+    JK_REQUIRE((f.layernorm != nullptr) == (f.cast_rows != nullptr) && (f.layernorm != nullptr) == (f.glu != nullptr) &&
+               (f.layernorm != nullptr) == (f.conv_qkv != nullptr) && (f.layernorm != nullptr) == (f.linear_scan != nullptr) &&
+               (f.layernorm != nullptr) == (f.norm_gate != nullptr) && (f.layernorm != nullptr) == (f.err_mixers != nullptr),
+               "runner_bind: a module's entries come together");
     g_bound = true;
     return JK_OK;
 }
@@ -233,20 +237,30 @@ int run_qkv(Run &r, const RunnerOp &op, const FusedNorm &fused) {
 
 int run_attention(Run &r, const RunnerOp &op) {
     const int T = r.st.ntok, nh = op.heads, nkvh = op.kv_heads, dh = op.head_dim, page = r.env.page_size;
+    const int dv = op.v_head_dim > 0 ? op.v_head_dim : dh;
     void *q, *o;
     if (int rc = r.slot(op.in_slot, (long long)r.elem() * T * nh * dh, &q, "the queries")) return rc;
-    if (int rc = r.slot(op.out_slot, (long long)r.elem() * T * nh * dh, &o, "attention's output")) return rc;
+    if (int rc = r.slot(op.out_slot, (long long)r.elem() * T * nh * dv, &o, "attention's output")) return rc;
+    const float *gate = nullptr;
+    if (op.gated) {
+        void *u;
+        if (int rc = r.slot(SLOT_TMP, 4LL * T * op.ld, &u, "the projection that holds attention's gate")) return rc;
+        gate = (const float *)u + op.g_off;
+    }
     const int *table = r.st.block_tables[op.cache_group];
     JK_REQUIRE(table != nullptr, "runner: attention reads the cache of group %d, whose block table the step lacks", op.cache_group);
     const int n_short = r.st.list_n[op.list_short], n_tiles = r.st.list_n[op.list_tiles];
     const int *short_rows = r.st.lists[op.list_short], *tiles = r.st.lists[op.list_tiles];
     const bool tc = !r.env.legacy_tensor_cores && g_fns.attention_tcgen05 != nullptr && jk::attention_tcgen05_takes(dh, page);
     bool fast = r.env.dtype == JK_BF16 && !r.env.plain_attention && (n_short > 0 || n_tiles > 0) && dh % 8 == 0 && dh <= 256;
+    // values of another size than the keys, a sink, a gate: the row kernel's
+    if (dv != dh || op.sink || op.gated) fast = false;
     if (fast && n_tiles > 0 && !(tc || g_fns.attention_prefill_supports(dh))) fast = false;
     if (!fast) {
         // one warp per (row, head): float32, and every shape the tensor-core kernels are not built for
         RUN(attention, g_fns.attention_rows(q, op.k_pages, op.v_pages, o, r.env.dtype, r.st.positions, r.st.row_req, table,
-                                            r.env.max_blocks, page, T, nh, nkvh, dh, op.softmax_scale, op.window, r.stream));
+                                            r.env.max_blocks, page, T, nh, nkvh, dh, op.softmax_scale, op.window, dv, op.sink, gate, op.ld,
+                                            r.stream));
         return JK_OK;
     }
     if (n_tiles > 0) {
@@ -321,6 +335,15 @@ int run_gate_up(Run &r, const RunnerOp &op, const FusedNorm &fused) {
     void *h, *act;
     if (int rc = r.slot(op.in_slot, (long long)r.elem() * T * d, &h, "gate/up's activations")) return rc;
     if (int rc = r.slot(op.out_slot, (long long)r.elem() * T * di, &act, "the feed-forward's inner activations")) return rc;
+    if (op.act != RUNNER_ACT_NONE && op.act != RUNNER_ACT_SILU) {
+        // a gate of another kind than silu: the product in float32, then the gated unit's own kernel
+        JK_REQUIRE(g_fns.glu != nullptr, "runner: a gated unit with activation %d needs the mixers module", op.act);
+        void *gu;
+        if (int rc = r.slot(SLOT_TMP, 4LL * T * 2 * di, &gu, "the gate/up product")) return rc;
+        if (int rc = product_f32(r, h, op.w, nullptr, (float *)gu, T, 2 * di, d)) return rc;
+        RUN(mixers, g_fns.glu((const float *)gu, act, r.env.dtype, T, di, op.act, r.stream));
+        return JK_OK;
+    }
     if (fused.norm != nullptr) {
         RUN(linear_small, g_fns.linear_small_norm(h, op.w, act, T, di, d, di, 1, fused.sumsq, fused.norm->eps, nullptr, nullptr, nullptr,
                                                   1.f, r.env.status, ro.sms, r.stream));
@@ -359,6 +382,77 @@ int run_linear(Run &r, const RunnerOp &op) {
     if (int rc = r.slot(op.in_slot, (long long)r.elem() * rows * op.k, &in, "a product's activations")) return rc;
     if (int rc = r.slot(op.out_slot, 4LL * rows * op.n, &out, "a product's output")) return rc;
     return product_f32(r, in, op.w, op.vec, (float *)out, rows, op.n, op.k);
+}
+
+// ---- records of csrc/mixers.cu -------------------------------------------------------------------------------
+int need_mixers(const char *what) {
+    JK_REQUIRE(g_fns.layernorm != nullptr, "runner: %s needs the mixers module, which was not bound", what);
+    return JK_OK;
+}
+
+int run_cast(Run &r, const RunnerOp &op) {
+    if (int rc = need_mixers("a cast of the stream")) return rc;
+    const int T = r.st.ntok;
+    void *out;
+    if (int rc = r.slot(op.out_slot, (long long)r.elem() * T * op.n, &out, "the stream as activations")) return rc;
+    if (int rc = flush_pending(r, T, op.n)) return rc;
+    RUN(mixers, g_fns.cast_rows(r.x(), out, r.env.dtype, (long long)T * op.n, r.stream));
+    return JK_OK;
+}
+
+int run_layernorm(Run &r, const RunnerOp &op) {
+    if (int rc = need_mixers("a layer norm")) return rc;
+    const int T = r.st.ntok;
+    if (op.in_slot == SLOT_DELTA) {         // the norm of a sublayer's output, added into the stream
+        void *delta, *h = nullptr;
+        if (int rc = r.slot(SLOT_DELTA, 4LL * T * op.n, &delta, "a sublayer's output")) return rc;
+        if (op.out_slot >= 0)
+            if (int rc = r.slot(op.out_slot, (long long)r.elem() * T * op.n, &h, "the stream as activations")) return rc;
+        JK_REQUIRE(!r.pending, "runner: a layer norm over a sublayer's output while another product waits to be added");
+        RUN(mixers, g_fns.layernorm((const float *)delta, nullptr, T, op.n, op.vec, op.bias, op.eps, r.x(), h, r.env.dtype, r.stream));
+        return JK_OK;
+    }
+    const int rows = op.wanted_rows ? r.st.n_want : T;
+    if (rows == 0) return JK_OK;
+    void *out;
+    if (int rc = r.slot(op.out_slot, (long long)r.elem() * rows * op.n, &out, "a norm")) return rc;
+    if (int rc = flush_pending(r, T, op.n)) return rc;
+    RUN(mixers, g_fns.layernorm(r.x(), op.wanted_rows ? r.st.want_rows : nullptr, rows, op.n, op.vec, op.bias, op.eps, nullptr, out,
+                                r.env.dtype, r.stream));
+    return JK_OK;
+}
+
+int run_conv_qkv(Run &r, const RunnerOp &op) {
+    if (int rc = need_mixers("a convolved q/k/v")) return rc;
+    const int T = r.st.ntok, dv = op.v_head_dim > 0 ? op.v_head_dim : op.head_dim;
+    void *u, *q;
+    if (int rc = r.slot(op.in_slot, 4LL * T * op.ld, &u, "the q/k/v projection")) return rc;
+    if (int rc = r.slot(op.out_slot, (long long)r.elem() * T * op.heads * op.head_dim, &q, "the queries")) return rc;
+    const int *table = op.has_kv ? r.st.block_tables[op.cache_group] : nullptr;
+    JK_REQUIRE(!op.has_kv || table != nullptr, "runner: q/k/v writes the cache of group %d, whose block table the step lacks", op.cache_group);
+    JK_REQUIRE(r.st.slot_ids != nullptr || op.state == nullptr, "runner: a convolution keeps tails, but the step names no state slots");
+    RUN(mixers, g_fns.conv_qkv((const float *)u, op.ld, op.q_off, op.k_off, op.v_off, op.heads, op.kv_heads, op.head_dim, dv, op.has_kv,
+                               op.conv_q, op.conv_k, op.conv_v, op.taps, op.norm_q, op.norm_k, op.eps, op.freq, op.rot_dims, op.state,
+                               r.st.positions, r.st.row_req, r.st.req_start, r.st.slot_ids, table, r.env.max_blocks, r.env.page_size, q,
+                               op.k_pages, op.v_pages, r.env.dtype, T, r.st.nreq, r.stream));
+    if (op.taps > 1) ++g_launches;      // the tails' kernel
+    return JK_OK;
+}
+
+int run_linear_attention(Run &r, const RunnerOp &op) {
+    if (int rc = need_mixers("a linear attention")) return rc;
+    const int T = r.st.ntok, dv = op.v_head_dim > 0 ? op.v_head_dim : op.head_dim;
+    void *u, *mix, *out;
+    if (int rc = r.slot(op.in_slot, 4LL * T * op.ld, &u, "the q/k/v projection")) return rc;
+    if (int rc = r.slot(SLOT_MIX, 4LL * T * op.heads * dv, &mix, "a recurrence's output")) return rc;
+    if (int rc = r.slot(op.out_slot, (long long)r.elem() * T * op.heads * dv, &out, "a linear attention's output")) return rc;
+    JK_REQUIRE(r.st.slot_ids != nullptr && op.state != nullptr, "runner: a recurrence without its state slots");
+    RUN(mixers, g_fns.linear_scan((const float *)u, op.ld, op.q_off, op.k_off, op.v_off, op.heads, op.head_dim, dv, op.act, op.q_scale,
+                                  op.decay, op.w2, r.env.dtype, op.b2, op.r_off, op.rank, op.tau, op.state, r.st.req_start, r.st.slot_ids,
+                                  r.st.nreq, T, (float *)mix, r.env.routing.sms, r.stream));
+    RUN(mixers, g_fns.norm_gate((const float *)mix, (const float *)u, op.ld, op.g_off, op.vec, op.eps, op.heads, dv, op.per_head_norm,
+                                op.gate_act, out, r.env.dtype, T, r.stream));
+    return JK_OK;
 }
 
 }  // namespace
@@ -422,6 +516,20 @@ JK_EXPORT int jk_runner_run(const RunnerEnv *envp, const RunnerOp *ops, int firs
             case OP_LINEAR:
                 rc = run_linear(r, op);
                 break;
+            case OP_CAST:
+                hidden = op.n;
+                rc = run_cast(r, op);
+                break;
+            case OP_LAYERNORM:
+                hidden = op.n;
+                rc = run_layernorm(r, op);
+                break;
+            case OP_CONV_QKV:
+                rc = run_conv_qkv(r, op);
+                break;
+            case OP_LINEAR_ATTENTION:
+                rc = run_linear_attention(r, op);
+                break;
             default:
                 JK_FAIL(JK_BAD_ARGUMENT, "runner_run: record %d has kind %d", i, op.kind);
         }
@@ -452,7 +560,8 @@ JK_EXPORT int jk_runner_slot_bytes(const RunnerEnv *env, const RunnerOp *ops, in
                 need(op.in_slot, e * rows * op.k); need(op.out_slot, e * rows * op.heads * op.head_dim); need(SLOT_TMP, 4 * rows * op.n);
                 break;
             case OP_ATTENTION: {
-                need(op.in_slot, e * rows * op.heads * op.head_dim); need(op.out_slot, e * rows * op.heads * op.head_dim);
+                need(op.in_slot, e * rows * op.heads * op.head_dim);
+                need(op.out_slot, e * rows * op.heads * (op.v_head_dim > 0 ? op.v_head_dim : op.head_dim));
                 // the worst step: more rows mean fewer cuts; every context bucket up to the longest
                 long long worst = 0;
                 for (int context = 256;; context *= 2) {
@@ -471,6 +580,17 @@ JK_EXPORT int jk_runner_slot_bytes(const RunnerEnv *env, const RunnerOp *ops, in
             case OP_RESIDUAL: need(op.in_slot, e * rows * op.k); need(SLOT_X, 4 * rows * op.n); need(SLOT_DELTA, 4 * rows * op.n); break;
             case OP_GATE_UP: need(op.in_slot, e * rows * op.k); need(op.out_slot, e * rows * op.n); need(SLOT_TMP, 4 * rows * 2 * op.n); break;
             case OP_LINEAR: need(op.in_slot, e * rows * op.k); need(op.out_slot, 4 * rows * op.n); break;
+            case OP_CAST: need(SLOT_X, 4 * rows * op.n); need(op.out_slot, e * rows * op.n); break;
+            case OP_LAYERNORM:
+                need(SLOT_X, 4LL * max_rows * op.n); need(op.in_slot, 4 * rows * op.n);
+                if (op.out_slot >= 0) need(op.out_slot, e * rows * op.n);
+                break;
+            case OP_CONV_QKV: need(op.in_slot, 4 * rows * op.ld); need(op.out_slot, e * rows * op.heads * op.head_dim); break;
+            case OP_LINEAR_ATTENTION: {
+                const long long width = (long long)op.heads * (op.v_head_dim > 0 ? op.v_head_dim : op.head_dim);
+                need(op.in_slot, 4 * rows * op.ld); need(SLOT_MIX, 4 * rows * width); need(op.out_slot, e * rows * width);
+                break;
+            }
             default: JK_FAIL(JK_BAD_ARGUMENT, "runner_slot_bytes: record %d has kind %d", i, op.kind);
         }
     }

@@ -30,7 +30,7 @@ typedef int (*GemmTcgen05Fn)(const void *, const void *, void *, int, int, int, 
 typedef int (*GemmTcgen05QkvFn)(const void *, const void *, int, int, void *, void *, void *, const float *, const float *,
                                 const int *, const int *, const int *, int, int, int, int, int, int *, int, cudaStream_t);
 typedef int (*AttentionRowsFn)(const void *, const void *, const void *, void *, int, const int *, const int *, const int *, int,
-                               int, int, int, int, int, float, int, cudaStream_t);
+                               int, int, int, int, int, float, int, int, int, const float *, int, cudaStream_t);
 typedef int (*AttentionDecodeFn)(const void *, const void *, const void *, void *, float *, const int *, int, const int *,
                                  const int *, const int *, int, int, int, int, int, float, int, int, cudaStream_t);
 typedef int (*AttentionPrefillFn)(const void *, const void *, const void *, void *, const int *, int, int, const int *,
@@ -45,6 +45,16 @@ typedef int (*LinearSmallQkvNormFn)(const void *, const void *, int, int, void *
                                     const int *, const int *, const int *, int, int, int, int, int,
                                     const unsigned long long *, float, int, cudaStream_t);
 typedef const char *(*LastErrorFn)();
+// csrc/mixers.cu
+typedef int (*LayernormFn)(const float *, const int *, int, int, const float *, const float *, float, float *, void *, int, cudaStream_t);
+typedef int (*CastRowsFn)(const float *, void *, int, long long, cudaStream_t);
+typedef int (*GluFn)(const float *, void *, int, int, int, int, cudaStream_t);
+typedef int (*ConvQkvFn)(const float *, int, int, int, int, int, int, int, int, int, const float *, const float *, const float *, int,
+                         const float *, const float *, float, const float *, int, float *, const int *, const int *, const int *,
+                         const int *, const int *, int, int, void *, void *, void *, int, int, int, cudaStream_t);
+typedef int (*LinearScanFn)(const float *, int, int, int, int, int, int, int, int, float, const float *, const void *, int, const float *,
+                            int, int, float, float *, const int *, const int *, int, int, float *, int, cudaStream_t);
+typedef int (*NormGateFn)(const float *, const float *, int, int, const float *, float, int, int, int, int, void *, int, int, cudaStream_t);
 typedef int (*ArgmaxFn)(const float *, long long, int, int, int *, void *, cudaStream_t);
 typedef int (*SampleFn)(const float *, long long, int, int, const float *, const int *, const float *, const float *, int *,
                         cudaStream_t);
@@ -79,6 +89,15 @@ struct RunnerFns {
     ArgmaxFn argmax;
     SampleFn sample;
     LastErrorFn err_sampling;
+    // layer norm, short convolutions, linear-attention recurrences and their companions (csrc/mixers.cu): bound together,
+    // and only for a model whose records name them
+    LayernormFn layernorm;
+    CastRowsFn cast_rows;
+    GluFn glu;
+    ConvQkvFn conv_qkv;
+    LinearScanFn linear_scan;
+    NormGateFn norm_gate;
+    LastErrorFn err_mixers;
 };
 
 // ---- records ---------------------------------------------------------------------------------------------------
@@ -96,6 +115,7 @@ enum RunnerSlot {
     SLOT_LOGITS,        // float32 [wanted rows, vocabulary]
     SLOT_TMP,           // float32: the product before an unfused rotation or activation ([T, widest such product])
     SLOT_DECODE,        // float32: partial results of the split-key attention
+    SLOT_MIX,           // float32 [T, heads * value size]: a recurrence's output before its norm and gate
     RUNNER_SLOTS
 };
 
@@ -107,7 +127,16 @@ enum RunnerOpKind {
     OP_RESIDUAL,        // stream += scale * (in w^T)   (left pending for the next norm where no kernel adds in place)
     OP_GATE_UP,         // out = silu(in w_gate^T) * (in w_up^T), w = [gate rows; up rows]
     OP_LINEAR,          // out (float32) = in w^T (+ bias)                                            rows: all | wanted
+    OP_CAST,            // out = activations(stream): the operand of a sublayer that reads the stream itself
+    OP_LAYERNORM,       // in = SLOT_DELTA: stream += LN(in) (and out = activations(stream) if out_slot >= 0);
+                        // in = SLOT_X: out = LN(stream[rows])                                        rows: all | wanted
+    OP_CONV_QKV,        // in: float32 rows [q | k | v | ...]; short convolution over time, RMS norm over the whole q and k,
+                        // partial rotation; q -> out, k and v -> their pages; the convolution's tails move forward
+    OP_LINEAR_ATTENTION,// in: float32 rows [q | k | v | gate | ...]; S = diag(a) S + k v^T, o = S^T q per head over each
+                        // request's rows and its state slot; out = rmsnorm(o) * w * act(gate)
 };
+
+enum RunnerAct { RUNNER_ACT_NONE = 0, RUNNER_ACT_SILU = 1, RUNNER_ACT_GELU_TANH = 2, RUNNER_ACT_SIGMOID = 3 };
 
 struct RunnerOp {
     int kind;
@@ -125,6 +154,28 @@ struct RunnerOp {
     const float *cos_table, *sin_table;     // [positions, head_dim / 2] or null
     void *k_pages, *v_pages;    // [pages, kv_heads, page_size, head_dim] in the compute type
     int num_pages;
+    // ---- what the mixers of csrc/mixers.cu add; all zero in the records of the plain decoder ----------------------
+    int v_head_dim;             // ATTENTION, CONV_QKV, LINEAR_ATTENTION: size of a value head (0: head_dim)
+    int sink;                   // ATTENTION: 1 adds a key of score 0 that has no value to every row's softmax
+    int gated;                  // ATTENTION: 1 multiplies head h's output by sigmoid(SLOT_TMP[t, g_off + h])
+    int act;                    // GATE_UP: RunnerAct of the gate (0 stands for silu); LINEAR_ATTENTION: of q, k and v
+    int gate_act;               // LINEAR_ATTENTION: RunnerAct of the output gate
+    int ld;                     // width of the fused projection's float32 rows that the record reads
+    int q_off, k_off, v_off, g_off, r_off;      // columns of queries, keys, values, gate and decay projection in those rows
+    int taps;                   // CONV_QKV: taps of the convolution (0: none)
+    int rot_dims;               // CONV_QKV: leading elements of each head that are rotated, in pairs (2i, 2i+1)
+    int per_head_norm;          // LINEAR_ATTENTION: 1 norms each head over its values (weight [dv]); 0 all heads at once
+    int rank;                   // LINEAR_ATTENTION: width of the decay's projection (0: a constant per head)
+    int has_kv;                 // CONV_QKV: 1 makes keys and values too (0: queries only, the cache is another layer's)
+    float tau, q_scale;         // LINEAR_ATTENTION: decay = sigmoid(z)^(1/tau); factor of q
+    const float *conv_q, *conv_k, *conv_v;      // CONV_QKV: [channels, taps]
+    const float *norm_q, *norm_k;               // CONV_QKV: weights of the whole-projection RMS norms
+    const float *freq;          // CONV_QKV: [rot_dims / 2] angle per position of each pair
+    const float *decay;         // LINEAR_ATTENTION: [heads] constant decays, or null
+    const void *w2;             // LINEAR_ATTENTION: [heads * head_dim, rank] in the compute type, or null
+    const float *b2;            // LINEAR_ATTENTION: [heads * head_dim]
+    const float *bias;          // LAYERNORM: the bias
+    float *state;               // CONV_QKV: tails [slots, taps - 1, channels]; LINEAR_ATTENTION: [slots, heads, dk, dv]
 };
 
 // What does not change from step to step and is no part's business.
@@ -143,6 +194,7 @@ struct RunnerStep {
     int ntok, nreq, n_want;
     int context;                // the context length the step is planned for (the bucket of the live lengths)
     const int *tokens, *positions, *row_req, *req_start, *req_pos, *want_rows;
+    const int *slot_ids;        // [nreq] the state slot of each request
     const int *block_tables[jk::MAX_CACHE_GROUPS];
     const int *lists[jk::MAX_STEP_LISTS];     // work lists that mixers asked for; null with n == ntok means "rows 0..ntok-1"
     int list_n[jk::MAX_STEP_LISTS];

@@ -24,7 +24,7 @@ import torch
 from ..cache import CacheManager, OutOfPages
 from ..config import read_config
 from ..kernels import host as host_rules
-from ..parts import Model, ProgramRunner, Runtime, StepContext, cache_needs, model_manifest
+from ..parts import Model, ProgramRunner, Runtime, StepContext, cache_needs, model_manifest, state_needs
 from ..weights import FileWeights, check_manifest
 
 
@@ -61,14 +61,14 @@ class Engine:
         weights.close()
         num_pages = (cache_tokens + page_size - 1) // page_size
         self.cache = CacheManager(cache_needs(spec), num_pages, page_size, max_requests,
-                                  spec.max_positions, dtype=dtype, device=self.device)
+                                  spec.max_positions, dtype=dtype, device=self.device, entry_states=state_needs(spec))
         self.max_requests = max_requests
         self.max_step_tokens = max_step_tokens
         self.use_graphs = use_graphs and self.model.graph_safe
         # The model as launch records (parts/program.py) and the buffers that a step replays them over.  With
         # ``native_runner=False`` (or JK_NO_RUNNER=1) every record is a call of its own, so that no record shares work
         # with its neighbours: the unfused way of running the same program.
-        self.program = self.model.plan(self.cache.views, page_size, self.cache.max_blocks)
+        self.program = self.model.plan(self.cache.views, page_size, self.cache.max_blocks, state_views=self.cache.state_views)
         one_by_one = not native_runner or os.environ.get("JK_NO_RUNNER") == "1"
         self.runner = ProgramRunner(self.program, max_step_tokens, one_by_one=one_by_one)
         # what the mixers ask every step to carry (work lists), after the arrays that every model needs

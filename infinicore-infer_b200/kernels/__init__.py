@@ -420,21 +420,33 @@ def _sm_count(device) -> int:
 
 def attention_rows(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor,
                    positions: torch.Tensor, row_req: torch.Tensor, block_table: torch.Tensor, ntok: int,
-                   nh: int, scale: float, window: int = 0) -> torch.Tensor:
-    """Causal attention of ``ntok`` query rows over the paged cache, one warp per (row, head)."""
+                   nh: int, scale: float, window: int = 0, sink: bool = False,
+                   gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Causal attention of ``ntok`` query rows over the paged cache, one warp per (row, head).  Values may have
+    another size than keys (``v_pages [..., dv]``, ``out [ntok, nh, dv]``); ``sink`` adds a key of score 0 without a
+    value; ``gate`` (float32 ``[ntok, >= nh]``, a view of wider rows is fine) multiplies head h's output by
+    sigmoid(gate[t, h])."""
     _need(q, "q"); _need(k_pages, "k_pages"); _need(v_pages, "v_pages"); _need(out, "out")
     _need(positions, "positions", torch.int32); _need(row_req, "row_req", torch.int32)
     _need(block_table, "block_table", torch.int32)
     if not (q.dtype == k_pages.dtype == v_pages.dtype == out.dtype):
         raise KernelError("attention: q, pages and out must have one type")
     _, nkvh, page_size, dh = k_pages.shape
-    if q.numel() < ntok * nh * dh or out.numel() < ntok * nh * dh:
+    dv = v_pages.shape[-1]
+    if q.numel() < ntok * nh * dh or out.numel() < ntok * nh * dv:
         raise KernelError("attention: q or out is too small")
+    gate_ld = 0
+    if gate is not None:
+        _need(gate, "gate", torch.float32, contiguous=False)
+        if gate.dim() != 2 or gate.stride(1) != 1 or gate.shape[0] < ntok or gate.shape[1] < nh:
+            raise KernelError("attention: gate must be [rows, heads] with unit stride along heads")
+        gate_ld = gate.stride(0)
     lib = _build.load("attention")
     _check("attention", lib.jk_attention_rows(
         _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _c_int(dtype_code(q.dtype)), _ptr(positions),
         _ptr(row_req), _ptr(block_table), _c_int(block_table.shape[1]), _c_int(page_size), _c_int(ntok),
-        _c_int(nh), _c_int(nkvh), _c_int(dh), _c_float(scale), _c_int(window or 0), _stream()))
+        _c_int(nh), _c_int(nkvh), _c_int(dh), _c_float(scale), _c_int(window or 0), _c_int(dv), _c_int(1 if sink else 0),
+        _ptr(gate), _c_int(gate_ld), _stream()))
     return out
 
 
@@ -521,6 +533,88 @@ def attention_tcgen05(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Ten
         _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(tiles), _c_int(ntiles), _c_int(ntok), _ptr(req_start),
         _ptr(req_pos), _ptr(block_table), _c_int(block_table.shape[1]), _c_int(num_pages), _c_int(page_size), _c_int(nh),
         _c_int(nkvh), _c_int(dh), _c_float(scale), _c_int(window or 0), _ptr(gemm_status(q.device)), _stream()))
+    return out
+
+
+# ---- csrc/mixers.cu ------------------------------------------------------------------------------------------------
+ACT_NONE, ACT_SILU, ACT_GELU_TANH, ACT_SIGMOID = 0, 1, 2, 3
+
+
+def layernorm(src: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], eps: float, out: Optional[torch.Tensor] = None,
+              rows: Optional[torch.Tensor] = None, add_into: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """``add_into`` given: add_into += LN(src), and ``out`` (if given) = add_into in its own type.  Otherwise
+    out[i] = LN(src[rows[i]]) (all rows without ``rows``).  src and add_into are float32 ``[T, d]``."""
+    _need(src, "src", torch.float32); _need(weight, "weight", torch.float32)
+    d = src.shape[-1]
+    n = rows.numel() if rows is not None else src.numel() // d
+    for t, name in ((bias, "bias"), (add_into, "add_into")):
+        if t is not None:
+            _need(t, name, torch.float32)
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+    if out is not None:
+        _need(out, "out")
+        if out.numel() < n * d:
+            raise KernelError("layernorm: out is too small")
+    lib = _build.load("mixers")
+    _check("mixers", lib.jk_layernorm(_ptr(src), _ptr(rows), _c_int(n), _c_int(d), _ptr(weight), _ptr(bias), _c_float(eps), _ptr(add_into),
+                                      _ptr(out), _c_int(dtype_code(out.dtype) if out is not None else F32), _stream()))
+    return out
+
+
+def glu(gate_up: torch.Tensor, out: torch.Tensor, act: int) -> torch.Tensor:
+    """out[t, c] = act(gate_up[t, c]) * gate_up[t, di + c]; gate_up float32."""
+    _need(gate_up, "gate_up", torch.float32); _need(out, "out")
+    ntok, di = out.shape
+    if gate_up.shape != (ntok, 2 * di):
+        raise KernelError(f"glu: gate_up {tuple(gate_up.shape)} for out {tuple(out.shape)}")
+    lib = _build.load("mixers")
+    _check("mixers", lib.jk_glu(_ptr(gate_up), _ptr(out), _c_int(dtype_code(out.dtype)), _c_int(ntok), _c_int(di), _c_int(act), _stream()))
+    return out
+
+
+def conv_qkv(u: torch.Tensor, offsets, heads: int, kv_heads: int, dk: int, dv: int, has_kv: bool, convs, taps: int, norms, eps: float,
+             freq: Optional[torch.Tensor], rot_dims: int, tail: Optional[torch.Tensor], positions, row_req, req_start, slot_ids,
+             block_table: Optional[torch.Tensor], page_size: int, q_out: torch.Tensor, k_pages=None, v_pages=None) -> torch.Tensor:
+    """Short convolution, whole-projection RMS norm, pair rotation and cache write of fused float32 projections ``u``
+    ``[T, ld]`` (columns ``offsets = (q, k, v)``); ``convs = (q, k, v)`` taps ``[channels, taps]`` or None each;
+    ``norms = (q, k)`` weights or None each; ``tail [slots, taps - 1, channels]`` is read and moved forward."""
+    _need(u, "u", torch.float32); _need(q_out, "q_out")
+    T, nreq = u.shape[0], req_start.numel() - 1
+    lib = _build.load("mixers")
+    _check("mixers", lib.jk_conv_qkv(
+        _ptr(u), _c_int(u.shape[1]), _c_int(offsets[0]), _c_int(offsets[1]), _c_int(offsets[2]), _c_int(heads), _c_int(kv_heads),
+        _c_int(dk), _c_int(dv), _c_int(1 if has_kv else 0), _ptr(convs[0]), _ptr(convs[1]), _ptr(convs[2]), _c_int(taps),
+        _ptr(norms[0]), _ptr(norms[1]), _c_float(eps), _ptr(freq), _c_int(rot_dims), _ptr(tail), _ptr(positions), _ptr(row_req),
+        _ptr(req_start), _ptr(slot_ids), _ptr(block_table), _c_int(block_table.shape[1] if block_table is not None else 0),
+        _c_int(page_size), _ptr(q_out), _ptr(k_pages), _ptr(v_pages), _c_int(dtype_code(q_out.dtype)), _c_int(T), _c_int(nreq), _stream()))
+    return q_out
+
+
+def linear_scan(u: torch.Tensor, offsets, heads: int, dk: int, dv: int, qkv_act: int, q_scale: float, decay: Optional[torch.Tensor],
+                w2: Optional[torch.Tensor], b2: Optional[torch.Tensor], r_off: int, tau: float, state: torch.Tensor,
+                req_start: torch.Tensor, slot_ids: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """S = diag(a) S + k v^T, o = S^T q over each request's rows of the fused float32 projections ``u`` (columns
+    ``offsets = (q, k, v)``), from and into ``state [slots, heads, dk, dv]``; ``out`` float32 ``[T, heads * dv]``."""
+    _need(u, "u", torch.float32); _need(state, "state", torch.float32); _need(out, "out", torch.float32)
+    T, nreq = u.shape[0], req_start.numel() - 1
+    lib = _build.load("mixers")
+    _check("mixers", lib.jk_linear_scan(
+        _ptr(u), _c_int(u.shape[1]), _c_int(offsets[0]), _c_int(offsets[1]), _c_int(offsets[2]), _c_int(heads), _c_int(dk), _c_int(dv),
+        _c_int(qkv_act), _c_float(q_scale), _ptr(decay), _ptr(w2), _c_int(dtype_code(w2.dtype) if w2 is not None else F32), _ptr(b2),
+        _c_int(r_off), _c_int(w2.shape[1] if w2 is not None else 0), _c_float(tau), _ptr(state), _ptr(req_start), _ptr(slot_ids),
+        _c_int(nreq), _c_int(T), _ptr(out), _c_int(_sm_count(u.device)), _stream()))
+    return out
+
+
+def norm_gate(o: torch.Tensor, u: torch.Tensor, g_off: int, weight: torch.Tensor, eps: float, heads: int, dv: int, per_head: bool,
+              gate_act: int, out: torch.Tensor) -> torch.Tensor:
+    """out = rmsnorm(o) * weight * act(u[:, g_off : g_off + heads * dv]); the norm over all heads or head by head."""
+    _need(o, "o", torch.float32); _need(u, "u", torch.float32); _need(weight, "weight", torch.float32); _need(out, "out")
+    lib = _build.load("mixers")
+    _check("mixers", lib.jk_norm_gate(_ptr(o), _ptr(u), _c_int(u.shape[1]), _c_int(g_off), _ptr(weight), _c_float(eps), _c_int(heads),
+                                      _c_int(dv), _c_int(1 if per_head else 0), _c_int(gate_act), _ptr(out), _c_int(dtype_code(out.dtype)),
+                                      _c_int(o.shape[0]), _stream()))
     return out
 
 

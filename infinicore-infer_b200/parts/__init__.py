@@ -7,8 +7,14 @@ from .rope import RotaryTables
 from .attention import Attention
 from .feed_forward import SwiGLU
 from .block import PreNormBlock
-from .model import Model, cache_needs, model_manifest
+from .layernorm import LayerNorm
+from .glu import GLU
+from .linear_attention import LinearAttention
+from .conv_attention import ConvAttention
+from .postnorm_block import PostNormBlock
+from .model import Model, cache_needs, model_manifest, state_needs
 
 __all__ = ["BLOCKS", "FEED_FORWARDS", "MIXERS", "NORMS", "POSITIONS", "ResidualStream", "Runtime", "StepContext", "Program",
            "ProgramRunner", "HostIO", "part_class", "register", "RMSNorm", "RotaryTables", "Attention", "SwiGLU",
-           "PreNormBlock", "Model", "cache_needs", "model_manifest"]
+           "PreNormBlock", "LayerNorm", "GLU", "LinearAttention", "ConvAttention", "PostNormBlock", "Model", "cache_needs", "model_manifest",
+           "state_needs"]

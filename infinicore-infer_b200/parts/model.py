@@ -42,9 +42,24 @@ def cache_needs(spec) -> List[object]:
             layer = spec.layers[e.layer]
             mine = part_class("block", layer).cache_need(layer)
             if mine != needs[e.cache]:
-                raise ValueError(f"layer {e.layer} reads cache {e.cache}, which holds {needs[e.cache]}, "
-                                 f"but needs {mine}")
+                # a reader with a mask of its own: the pages are kept for the widest window among the cache's users
+                both = needs[e.cache].shared_with(mine) if hasattr(needs[e.cache], "shared_with") else None
+                if both is None:
+                    raise ValueError(f"layer {e.layer} reads cache {e.cache}, which holds {needs[e.cache]}, "
+                                     f"but needs {mine}")
+                needs[e.cache] = both
     return needs
+
+
+def state_needs(spec) -> List[object]:
+    """What each entry of the run order keeps for itself beside its cache (``StateSlot`` or None), asked of the block
+    class's ``state_need(spec, writes_cache)`` where it has one."""
+    out: List[object] = []
+    for e in spec.order:
+        layer = spec.layers[e.layer]
+        ask = getattr(part_class("block", layer), "state_need", None)
+        out.append(ask(layer, e.writes_cache) if ask is not None else None)
+    return out
 
 
 class Model:
@@ -71,7 +86,7 @@ class Model:
             total += getattr(self.layers[e.layer], "weight_bytes", lambda: 0)()
         return total
 
-    def plan(self, views, page_size: int, max_blocks: int) -> Program:
+    def plan(self, views, page_size: int, max_blocks: int, state_views=None) -> Program:
         """The whole model as a program: the embedding, the layers in their run order, the final norm over the wanted
         rows with the logit scale riding on it (as in the reference, scripts/jiuge.py:198-201), the output product."""
         import ctypes
@@ -81,10 +96,14 @@ class Model:
         program.emit("jk_emit_embedding", ctypes.c_void_p(self.embedding.data_ptr()), ctypes.c_int(kernels.dtype_code(self.embedding.dtype)),
                      ctypes.c_int(spec.hidden_size), ctypes.c_float(spec.embed_scale), keep=(self.embedding,))
         hidden = spec.hidden_size
-        for e in spec.order:
+        for index, e in enumerate(spec.order):
             layer, view = self.layers[e.layer], views[e.cache]
+            own = state_views[index] if state_views else None
             if hasattr(layer, "plan"):
-                layer.plan(program, view, e.writes_cache)
+                if own is not None or hasattr(type(layer), "state_need"):
+                    layer.plan(program, view, e.writes_cache, state_view=own)
+                else:
+                    layer.plan(program, view, e.writes_cache)
             else:
                 program.host(_host_block(layer, view, e.writes_cache, hidden))
         if hasattr(self.final_norm, "plan"):

@@ -24,9 +24,13 @@ from ..kernels import host as _host
 
 _i, _f, _p, _ll = ctypes.c_int, ctypes.c_float, ctypes.c_void_p, ctypes.c_longlong
 
-SLOTS = ("x", "delta", "h", "q", "o", "act", "hw", "logits", "tmp", "decode")       # RunnerSlot of csrc/runner.h
+SLOTS = ("x", "delta", "h", "q", "o", "act", "hw", "logits", "tmp", "decode", "mix")       # RunnerSlot of csrc/runner.h
 SLOT = {name: i for i, name in enumerate(SLOTS)}
-OP_NAMES = {1: "embed", 2: "norm", 3: "qkv", 4: "attention", 5: "residual", 6: "gate_up", 7: "linear"}
+OP_NAMES = {1: "embed", 2: "norm", 3: "qkv", 4: "attention", 5: "residual", 6: "gate_up", 7: "linear", 8: "cast",
+            9: "layernorm", 10: "conv_qkv", 11: "linear_attention"}
+OP = {name: kind for kind, name in OP_NAMES.items()}                                # RunnerOpKind
+ACT = {"none": 0, "silu": 1, "gelu_tanh": 2, "sigmoid": 3}                          # RunnerAct
+_MIXERS_OPS = (OP["cast"], OP["layernorm"], OP["conv_qkv"], OP["linear_attention"])
 MAX_GROUPS = 8
 MAX_LISTS = 8
 
@@ -37,7 +41,12 @@ class RunnerOp(ctypes.Structure):
                                    "max_positions")]
                 + [(n, _f) for n in ("eps", "scale", "softmax_scale")]
                 + [(n, _p) for n in ("w", "vec", "cos_table", "sin_table", "k_pages", "v_pages")]
-                + [("num_pages", _i)])
+                + [("num_pages", _i)]
+                # what the mixers of csrc/mixers.cu add (all zero in the records of the plain decoder)
+                + [(n, _i) for n in ("v_head_dim", "sink", "gated", "act", "gate_act", "ld", "q_off", "k_off", "v_off", "g_off", "r_off",
+                                     "taps", "rot_dims", "per_head_norm", "rank", "has_kv")]
+                + [(n, _f) for n in ("tau", "q_scale")]
+                + [(n, _p) for n in ("conv_q", "conv_k", "conv_v", "norm_q", "norm_k", "freq", "decay", "w2", "b2", "bias", "state")])
 
 
 class Routing(ctypes.Structure):
@@ -52,7 +61,7 @@ class RunnerEnv(ctypes.Structure):
 
 class RunnerStep(ctypes.Structure):
     _fields_ = ([(n, _i) for n in ("ntok", "nreq", "n_want", "context")]
-                + [(n, _p) for n in ("tokens", "positions", "row_req", "req_start", "req_pos", "want_rows")]
+                + [(n, _p) for n in ("tokens", "positions", "row_req", "req_start", "req_pos", "want_rows", "slot_ids")]
                 + [("block_tables", _p * MAX_GROUPS), ("lists", _p * MAX_LISTS), ("list_n", _i * MAX_LISTS)])
 
 
@@ -67,26 +76,28 @@ class _Fns(ctypes.Structure):
         "gemm_tcgen05_qkv", "attention_rows", "attention_decode", "attention_prefill", "attention_prefill_supports",
         "attention_tcgen05", "err_elementwise", "err_linear_small", "err_gemm_tcgen05", "err_attention", "err_attention_tcgen05",
         "linear_small_supports", "linear_small_qkv_supports", "gemm_skinny", "linear_small_norm_supports", "linear_small_norm",
-        "linear_small_qkv_norm", "argmax", "sample", "err_sampling")]
+        "linear_small_qkv_norm", "argmax", "sample", "err_sampling", "layernorm", "cast_rows", "glu", "conv_qkv", "linear_scan",
+        "norm_gate", "err_mixers")]
 
 
 def _addr(lib, name: str) -> int:
     return ctypes.cast(getattr(lib, name), ctypes.c_void_p).value
 
 
-_bound: Dict[str, bool] = {"base": False, "gemm_tcgen05": False, "attention_tcgen05": False}
+_bound: Dict[str, bool] = {"base": False, "gemm_tcgen05": False, "attention_tcgen05": False, "mixers": False}
 
 
-def runner_lib(gemm_tcgen05: bool = False, attention_tcgen05: bool = False) -> ctypes.CDLL:
-    """The native step's library with the kernel modules' entry points handed over.  The tcgen05 modules are bound (and so
-    compiled) only when asked for: a model whose steps never reach them never builds them."""
+def runner_lib(gemm_tcgen05: bool = False, attention_tcgen05: bool = False, mixers: bool = False) -> ctypes.CDLL:
+    """The native step's library with the kernel modules' entry points handed over.  The tcgen05 modules and the module of
+    the mixers beyond softmax attention are bound (and so compiled) only when asked for: a model whose steps never reach
+    them never builds them."""
     lib = _build.load("runner")
-    want = {"base": True, "gemm_tcgen05": gemm_tcgen05, "attention_tcgen05": attention_tcgen05}
+    want = {"base": True, "gemm_tcgen05": gemm_tcgen05, "attention_tcgen05": attention_tcgen05, "mixers": mixers}
     if all(_bound[k] or not want[k] for k in want):
         return lib
     lib.jk_runner_last_error.restype = ctypes.c_char_p
     names = ["elementwise", "linear_small", "attention", "sampling"] + (["gemm_tcgen05"] if gemm_tcgen05 else []) \
-        + (["attention_tcgen05"] if attention_tcgen05 else [])
+        + (["attention_tcgen05"] if attention_tcgen05 else []) + (["mixers"] if mixers else [])
     mods = {m: _build.load(m) for m in names}
     get = lambda module, name: _addr(mods[module], name) if module in mods else None
     fns = _Fns(
@@ -112,7 +123,10 @@ def runner_lib(gemm_tcgen05: bool = False, attention_tcgen05: bool = False) -> c
         err_attention_tcgen05=get("attention_tcgen05", "jk_attention_tcgen05_last_error"),
         # the C interface of the same library (csrc/model_api.h) samples through these
         argmax=get("sampling", "jk_argmax"), sample=get("sampling", "jk_sample"),
-        err_sampling=get("sampling", "jk_sampling_last_error"))
+        err_sampling=get("sampling", "jk_sampling_last_error"),
+        layernorm=get("mixers", "jk_layernorm"), cast_rows=get("mixers", "jk_cast_rows"), glu=get("mixers", "jk_glu"),
+        conv_qkv=get("mixers", "jk_conv_qkv"), linear_scan=get("mixers", "jk_linear_scan"), norm_gate=get("mixers", "jk_norm_gate"),
+        err_mixers=get("mixers", "jk_mixers_last_error"))
     if lib.jk_runner_bind(ctypes.byref(fns)):
         from ..kernels import KernelError
         raise KernelError(lib.jk_runner_last_error().decode(errors="replace"))
@@ -130,6 +144,25 @@ def check_struct_sizes(lib) -> None:
         raise RuntimeError(f"the records' layout differs between Python {mine} and csrc/runner.h {list(sizes)}")
 
 
+def record(kind: str, in_slot: str = None, out_slot: str = None, **fields) -> RunnerOp:
+    """A launch record of ``kind`` (a name of ``OP_NAMES``) with the named fields set; tensors are given as tensors (their
+    address is taken; None is a null pointer), slots by name.  Fields that are not named are zero, ``scale`` is 1."""
+    op = RunnerOp()
+    op.kind = OP[kind]
+    op.in_slot = SLOT[in_slot] if in_slot is not None else -1
+    op.out_slot = SLOT[out_slot] if out_slot is not None else -1
+    op.scale = 1.0
+    for name, value in fields.items():
+        if isinstance(value, torch.Tensor):
+            value = value.data_ptr()
+        elif isinstance(value, bool):
+            value = int(value)
+        if not hasattr(op, name):
+            raise AttributeError(f"a launch record has no field {name}")
+        setattr(op, name, value)
+    return op
+
+
 class HostIO:
     """What a host step sees of a step's buffers: torch views of the slots for the rows of this step."""
 
@@ -140,7 +173,7 @@ class HostIO:
         """``[rows, width]`` of a slot (the activations' type unless said otherwise; ``x`` and ``delta`` are float32)."""
         rows = self.rows if rows is None else rows
         if dtype is None:
-            dtype = torch.float32 if slot in ("x", "delta", "logits", "tmp", "decode") else self._runner.runtime.dtype
+            dtype = torch.float32 if slot in ("x", "delta", "logits", "tmp", "decode", "mix") else self._runner.runtime.dtype
         raw = self._runner.slot_tensor(slot)
         need = rows * width * torch.empty((), dtype=dtype).element_size()
         if need > raw.numel():
@@ -162,6 +195,10 @@ class Program:
         self.keep: List[object] = []          # tensors that the records point into
         self.lists: Dict[str, int] = {}       # name of a work list -> its index in a step's lists
         self.list_owners: List[type] = []     # mixer classes whose work lists the steps must carry
+        # True while the activations slot holds the stream itself (in the activation type): what a sublayer that reads the
+        # stream takes as its operand.  Whoever emits records after that writes the slot, so emitting clears the mark; the
+        # part that leaves the slot so sets it again.
+        self.h_holds_stream = False
         check_struct_sizes(self.lib)
 
     # ---- emitting ----------------------------------------------------------------------------------------------------
@@ -180,6 +217,7 @@ class Program:
         else:
             self.items.append(("ops", self.count, n))
         self.count += n
+        self.h_holds_stream = False
 
     def emit(self, emitter: str, *args, keep=()) -> None:
         """Call a native emitter (``jk_emit_*`` of csrc/runner.cu) that writes its records at the program's end."""
@@ -187,10 +225,21 @@ class Program:
         self._emitted(fn(self._room(8), *args))
         self.keep.extend(keep)
 
+    def emit_records(self, records, keep=()) -> None:
+        """Append records that a part filled in by itself (``RunnerOp`` structures; ``record(kind, ...)`` makes one): how a
+        part whose operations exist as record kinds, but for which the native side has no emitter, says what it does."""
+        n = len(records)
+        self._room(n)
+        for j, rec in enumerate(records):
+            ctypes.memmove(ctypes.byref(self.ops, ctypes.sizeof(RunnerOp) * (self.count + j)), ctypes.byref(rec), ctypes.sizeof(RunnerOp))
+        self._emitted(n)
+        self.keep.extend(keep)
+
     def host(self, fn: Callable) -> None:
         """A step of the model that its own Python code runs: ``fn(ctx, io)`` with ``io`` a ``HostIO``.  The stream is
         whole when it is called (no product waits for its addition) and must be whole when it returns."""
         self.items.append(("host", fn))
+        self.h_holds_stream = False
 
     def work_lists(self, owner: type, names) -> List[int]:
         """Indices, in a step's lists, of the work lists that the mixer class ``owner`` fills for every step."""
@@ -239,7 +288,9 @@ class ProgramRunner:
         need_attn = rt.dtype == torch.bfloat16 and not rt.legacy_tensor_cores and any(
             program.ops[i].kind == 4 and _host.attention_tcgen05_takes(program.ops[i].head_dim, program.page_size)
             for i in range(program.count))
-        self.lib = runner_lib(need_gemm, need_attn)
+        need_mixers = any(program.ops[i].kind in _MIXERS_OPS or (program.ops[i].kind == OP["gate_up"] and program.ops[i].act > ACT["silu"])
+                          for i in range(program.count))
+        self.lib = runner_lib(need_gemm, need_attn, need_mixers)
         self.lib.jk_runner_last_error.restype = ctypes.c_char_p
         sizes = (_ll * len(SLOTS))()
         self._check(self.lib.jk_runner_slot_bytes(ctypes.byref(self.env), program.ops, program.count, max_rows, self.max_want, sizes))
@@ -283,7 +334,8 @@ class ProgramRunner:
         self.buffers.bytes[SLOT["logits"]] = logits.numel() * 4
         step = RunnerStep(ntok=T, nreq=ctx.nreq, n_want=n_want, context=ctx.context,
                           tokens=ctx.tokens.data_ptr(), positions=ctx.positions.data_ptr(), row_req=ctx.row_req.data_ptr(),
-                          req_start=ctx.req_start.data_ptr(), req_pos=ctx.req_pos.data_ptr(), want_rows=ctx.want_rows.data_ptr())
+                          req_start=ctx.req_start.data_ptr(), req_pos=ctx.req_pos.data_ptr(), want_rows=ctx.want_rows.data_ptr(),
+                          slot_ids=ctx.slot_ids.data_ptr())
         for g, table in enumerate(ctx.block_tables):
             step.block_tables[g] = table.data_ptr()
         for name, index in prog.lists.items():
@@ -332,7 +384,7 @@ def step_lists_for(owners, ctx, device) -> Dict[str, tuple]:
     return out
 
 
-def run_part_alone(runtime, plan, ctx, h: torch.Tensor, hidden_size: int, page_size: int = 16) -> torch.Tensor:
+def run_part_alone(runtime, plan, ctx, h: torch.Tensor, hidden_size: int, page_size: int = 16, result_slot: str = "x") -> torch.Tensor:
     """A mixer or feed-forward by itself: its records (emitted by ``plan(program)`` with a residual scale of 1) run
     over the activations ``h`` into a stream of zeros, which is then the part's output, float32 ``[T, hidden]``.
     For tests of a part alone and for blocks arranged by hand; a model runs its parts' records in one program."""
@@ -355,7 +407,7 @@ def run_part_alone(runtime, plan, ctx, h: torch.Tensor, hidden_size: int, page_s
     from .. import kernels
     step = RunnerStep(ntok=T, nreq=ctx.nreq, n_want=0, context=ctx.context, tokens=ctx.tokens.data_ptr(),
                       positions=ctx.positions.data_ptr(), row_req=ctx.row_req.data_ptr(), req_start=ctx.req_start.data_ptr(),
-                      req_pos=ctx.req_pos.data_ptr(), want_rows=None)
+                      req_pos=ctx.req_pos.data_ptr(), want_rows=None, slot_ids=ctx.slot_ids.data_ptr())
     for g, table in enumerate(ctx.block_tables):
         step.block_tables[g] = table.data_ptr()
     for name, index in program.lists.items():
@@ -365,4 +417,4 @@ def run_part_alone(runtime, plan, ctx, h: torch.Tensor, hidden_size: int, page_s
     runner._check(runner.lib.jk_runner_run(ctypes.byref(runner.env), program.ops, 0, program.count, ctypes.byref(step),
                                           ctypes.byref(runner.buffers), 1, kernels._stream()))
     kernels.launch_count += runner.lib.jk_runner_launches()
-    return x.clone()
+    return io.view(result_slot, hidden_size).clone()

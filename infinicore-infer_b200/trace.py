@@ -23,6 +23,7 @@ import os
 import sys
 
 PAGE_SIZE = 16       # divides 64, so a pool of N tokens holds every request rounded up to 64
+LIVE_REQUESTS = 4    # state slots: a trace never has more requests live at a time
 
 
 def replay(engine, records, out_dir=None, on_done=None):
@@ -73,6 +74,7 @@ def main(argv=None) -> int:
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens live requests hold at any time (each rounded up to 64)")
     ap.add_argument("--page-size", type=int, default=PAGE_SIZE)
+    ap.add_argument("--requests", type=int, default=LIVE_REQUESTS, help="state slots: most requests live at a time")
     ap.add_argument("--no-graphs", action="store_true", help="run decode steps without CUDA graphs")
     args = ap.parse_args(argv)
 
@@ -83,8 +85,10 @@ def main(argv=None) -> int:
     dtype = torch.bfloat16 if args.dtype == "bfloat16" else torch.float32
     cache_tokens = max(64, (args.max_tokens + 63) // 64 * 64)
     print(f"[trace_run] loading {args.model} in {args.dtype}", file=sys.stderr, flush=True)
-    engine = Engine.from_folder(args.model, dtype=dtype, device="cuda:0", cache_tokens=cache_tokens,
-                                page_size=args.page_size, max_requests=16,
+    # no request of the trace is longer than the pool, so the pool's size also serves as the longest sequence (a model
+    # whose configuration names none needs one for its block tables)
+    engine = Engine.from_folder(args.model, dtype=dtype, device="cuda:0", max_tokens=cache_tokens, cache_tokens=cache_tokens,
+                                page_size=args.page_size, max_requests=args.requests,
                                 max_step_tokens=cache_tokens, use_graphs=not args.no_graphs)
     print("[trace_run] ready", file=sys.stderr, flush=True)
     replay(engine, _records(sys.stdin), args.out, on_done=lambda s: print(f"done {s}", flush=True))

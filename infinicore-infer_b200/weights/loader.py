@@ -34,7 +34,7 @@ class TensorDecl:
     shape: Tuple[int, ...]
     role: str = MATRIX
     optional: bool = False
-    init: str = "normal"      # random-weights mode: "normal" N(0, std) or "ones" 1 + N(0, norm_std)
+    init: str = "normal"      # random-weights mode: "normal" N(0, std), "ones" 1 + N(0, norm_std), "zeros" N(0, norm_std), "taps" N(0, 0.5)
 
 
 class WeightError(ValueError):

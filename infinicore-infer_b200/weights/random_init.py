@@ -32,6 +32,10 @@ def _make(name: str, decl: TensorDecl, seed: int, std: float, norm_std: float, d
     x = torch.randn(decl.shape, generator=g, device=device, dtype=torch.float32)
     if decl.init == "ones":
         return 1.0 + norm_std * x
+    if decl.init == "zeros":          # biases: small values around zero
+        return norm_std * x
+    if decl.init == "taps":           # a short convolution's taps: of the order of one whatever the matrices' spread
+        return 0.5 * x
     return std * x
 
 
