@@ -200,14 +200,14 @@ def time_records(engine, ctx, which, repeats=3):
     runner.buffers.bytes[SLOT["logits"]] = logits.numel() * 4
     step = RunnerStep(ntok=T, nreq=ctx.nreq, n_want=ctx.want_rows.numel(), context=ctx.context, tokens=ctx.tokens.data_ptr(),
                       positions=ctx.positions.data_ptr(), row_req=ctx.row_req.data_ptr(), req_start=ctx.req_start.data_ptr(),
-                      req_pos=ctx.req_pos.data_ptr(), want_rows=ctx.want_rows.data_ptr())
+                      req_pos=ctx.req_pos.data_ptr(), want_rows=ctx.want_rows.data_ptr(), slot_ids=ctx.slot_ids.data_ptr())
     for g, table in enumerate(ctx.block_tables):
         step.block_tables[g] = table.data_ptr()
     for name, index in prog.lists.items():
         view, n = ctx.lists[name]
         step.lists[index] = view.data_ptr() if view is not None else None
         step.list_n[index] = n
-    indices = [i for i in (which(l) for l in range(len(engine.spec.order))) if i is not None]
+    indices = which if isinstance(which, (list, tuple)) else [i for i in (which(l) for l in range(len(engine.spec.order))) if i is not None]
 
     def walk():
         stream = kernels._stream()          # asked for at each walk: a capture runs on a stream of its own
@@ -236,6 +236,179 @@ def time_records(engine, ctx, which, repeats=3):
     return best
 
 
+# ---- --design: another architecture beside the decoder of the same size ------------------------------------------------
+# Layer sizes that resemble a real model's: (name, width, feed-forward, heads, key/value heads, head size, vocabulary).
+DESIGN_SIZES = {"2k": (2048, 5632, 16, 4, 128, 32000), "4k": (4096, 11008, 32, 8, 128, 32000)}
+F32_FMA_TFLOPS = 148 * 128 * 2 * 1.965e9 / 1e12      # nominal float32 rate of the CUDA cores (no measured figure exists)
+
+
+def sitelorn_shape(width, ff, heads, kv_heads, dim, vocab, window, layers=8):
+    """Eight layers in the order lightning, gla, attention, lightning, lightning, gla, attention on layer 2's keys,
+    lightning: heads of ``dim`` for keys and values everywhere, a window of ``window``, four taps."""
+    mlp = {"kind": "dense", "ff": ff}
+    light = {"type": "lightning", "mixer": {"heads": heads, "dim": dim, "vdim": dim,
+                                            "decay": [1.0 - 2.0 ** (-5 - 3 * h / max(1, heads - 1)) for h in range(heads)]}, "mlp": mlp}
+    gla = {"type": "gla", "mixer": {"heads": heads, "dim": dim, "vdim": dim, "tau": 16.0, "rank": 16}, "mlp": mlp}
+    att = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "conv": 4, "rot": {"dims": dim // 2, "base": 5e5},
+           "scale": dim ** -0.5, "mask": {"size": window}}
+    order = [light, gla, {"type": "attention", "mixer": att, "mlp": mlp}, light, light, gla,
+             {"type": "attention", "mixer": dict(att, kv_from=2), "mlp": mlp}, light]
+    return {"architecture": "Sitelorn", "embedding": {"scale": 1.0}, "norm": {"eps": 1e-5}, "vocab": vocab, "width": width,
+            "layers": order[:layers]}
+
+
+def decoder_shape(width, ff, heads, kv_heads, dim, vocab, layers=8):
+    return dict(model_type="llama", num_hidden_layers=layers, hidden_size=width, num_attention_heads=heads, num_key_value_heads=kv_heads,
+                head_dim=dim, intermediate_size=ff, vocab_size=vocab, max_position_embeddings=4096, rms_norm_eps=1e-5,
+                rope_theta=10000.0, tie_word_embeddings=False)
+
+
+def record_cost(op, T, B, context, decode, page_bytes):
+    """(bytes a record must move, floating-point operations it must do) for a step of T rows of B requests."""
+    from infinicore_infer_b200.parts.program import OP_NAMES
+    kind = OP_NAMES.get(op.kind)
+    dv = op.v_head_dim or op.head_dim
+    if kind in ("linear", "qkv", "residual"):
+        rows = T if not op.wanted_rows else B
+        return 2 * op.n * op.k + 2 * rows * op.k + 4 * rows * op.n, 2.0 * rows * op.n * op.k
+    if kind == "gate_up":
+        return 2 * 2 * op.n * op.k + 2 * T * op.k + 2 * T * op.n, 2.0 * T * 2 * op.n * op.k
+    if kind == "attention":
+        reach = min(context, op.window) if op.window else context
+        keys = B * reach if decode else T       # cached rows that are read at least once
+        seen = (B * reach) if decode else sum(min(t + 1, reach) for t in range(T))
+        return keys * op.kv_heads * (op.head_dim + dv) * 2 + 2 * T * op.heads * (op.head_dim + dv), 2.0 * seen * op.heads * (op.head_dim + dv)
+    if kind == "linear_attention":
+        state = B * op.heads * op.head_dim * dv * 4 * 2
+        return state + 4 * T * op.ld + 2 * T * op.heads * dv, 4.0 * T * op.heads * op.head_dim * dv
+    if kind == "conv_qkv":
+        return 4 * T * op.ld + 2 * T * (op.heads * op.head_dim + (op.kv_heads * (op.head_dim + dv) if op.has_kv else 0)), 0.0
+    if kind in ("layernorm", "norm"):
+        return T * op.n * (4 + 4 + 4 + 2), 0.0
+    if kind == "cast":
+        return T * op.n * 6, 0.0
+    return 0, 0.0
+
+
+def run_design(args):
+    """Prefill and decode of the Sitelorn design at layer sizes of real models beside the decoder (llama graph) of the same
+    width, feed-forward, heads and layer count, and every kind of launch record of both timed alone against its roofline.
+    Prints one JSON line of its own kind; the default benchmark is untouched."""
+    import torch
+    from infinicore_infer_b200.config import MiniCPMConfig, SitelornConfig
+    from infinicore_infer_b200.engine import Engine, StepEntry
+    from infinicore_infer_b200.parts import model_manifest
+    from infinicore_infer_b200.parts.program import OP_NAMES
+    from infinicore_infer_b200.weights import DeviceRandomWeights
+    from infinicore_infer_b200 import kernels
+
+    peaks, peak_source = load_peaks()
+    dev, page = "cuda:0", 16
+    T, B, context = args.design_prompt, args.batch, args.design_context
+    out = {"design": args.design, "peak_source": peak_source, "peak_hbm_gbs": peaks["hbm_gbs"], "peak_bf16_tflops": peaks["bf16_tflops"],
+           "f32_fma_tflops_nominal": round(F32_FMA_TFLOPS, 1), "prompt": T, "decode_batch": B, "decode_context": context,
+           "window": args.design_window, "dtype": "bf16", "data": "synthetic: random-init weights, random token ids, synthetic cache", "sizes": {}}
+    gen = torch.Generator().manual_seed(0)
+    with ClockSampler() as clocks:
+        for size in args.design_sizes.split(","):
+            width, ff, heads, kv_heads, dim, vocab = DESIGN_SIZES[size]
+            block = out["sizes"][size] = {"width": width, "ff": ff, "heads": heads, "kv_heads": kv_heads, "head_dim": dim, "layers": 8}
+            for which in ("sitelorn", "decoder"):
+                if which == "sitelorn":
+                    cfg = SitelornConfig.from_dict(sitelorn_shape(width, ff, heads, kv_heads, dim, vocab, args.design_window),
+                                                   max_tokens=max(4096, context + page))
+                else:
+                    cfg = MiniCPMConfig.from_dict(decoder_shape(width, ff, heads, kv_heads, dim, vocab))
+                spec = cfg.model_spec()
+                weights = DeviceRandomWeights(model_manifest(spec), seed=0, compute_dtype=torch.bfloat16, device=dev, std=0.02, untied=True)
+                engine = Engine(spec, weights, dtype=torch.bfloat16, device=dev, cache_tokens=max(B * (context + page), T + 4 * page),
+                                page_size=page, max_requests=B, max_step_tokens=max(T, 256))
+                for view in engine.cache.views:
+                    if hasattr(view, "k_pages"):
+                        view.k_pages.normal_(0, 0.5); view.v_pages.normal_(0, 0.5)
+                V = spec.vocab_size
+                res = block[which] = {}
+                # prefill: one prompt of T tokens, the best of three after a warm-up
+                ptoks = torch.randint(0, V, (T,), generator=gen).tolist()
+                times = []
+                for i in range(4):
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    torch.cuda.synchronize()
+                    e0.record()
+                    engine.step([StepEntry(f"p{i}", ptoks, [T - 1])])
+                    e1.record()
+                    torch.cuda.synchronize()
+                    engine.end(f"p{i}")
+                    if i:
+                        times.append(e0.elapsed_time(e1))
+                res["prefill_ms"] = round(min(times), 3)
+                res["prefill_tok_s"] = round(T * 1000.0 / min(times), 1)
+                # decode: B requests whose caches hold about `context` positions
+                steps, warm = args.steps, max(3, args.warmup)
+                start = context - steps - warm - 1
+                ids = [f"d{i}" for i in range(B)]
+                for r in ids:
+                    engine.begin(r); engine.cache.reserve(r, start); engine.cache.commit(r, start)
+                entries = [StepEntry(r, [int(t)], [0]) for r, t in zip(ids, torch.randint(0, V, (B,), generator=gen))]
+                arg = torch.empty(B, dtype=torch.int32, device=dev)
+                for _ in range(warm):
+                    kernels.argmax(engine.step(entries), arg)
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                l0 = engine.kernel_launches
+                e0.record()
+                for _ in range(steps):
+                    kernels.argmax(engine.step(entries), arg)
+                e1.record()
+                torch.cuda.synchronize()
+                ms = e0.elapsed_time(e1) / steps
+                res["decode_ms"] = round(ms, 4)
+                res["decode_tok_s"] = round(B * 1000.0 / ms, 1)
+                res["decode_launches_per_step"] = (engine.kernel_launches - l0) // steps
+                engine.check()
+                # every kind of record alone, decode then prefill
+                prog = engine.program
+                if not args.no_kernels:
+                    pos = engine.cache.length(ids[0])
+                    for r in ids:
+                        engine.cache.reserve(r, pos + 1)
+                    dctx = engine._upload(entries, [pos] * B, B, B)
+                    engine.begin("kp"); engine.cache.reserve("kp", T)
+                    pctx = engine._upload([StepEntry("kp", ptoks, [T - 1])], [0], 1, T)
+                    names, layer_of, layer = {}, [], -1
+                    for i in range(prog.count):
+                        kind = OP_NAMES.get(prog.ops[i].kind)
+                        if kind in ("embed",):
+                            continue
+                        op = prog.ops[i]
+                        key = f"{kind}:{op.n}x{op.k}" if kind in ("linear", "gate_up", "residual", "qkv") else \
+                            (f"{kind}:{'projected' if op.rank else 'constant'}" if kind == "linear_attention" else kind)
+                        names.setdefault(key, []).append(i)
+                    kern = res["records"] = {}
+                    for key, idx in names.items():
+                        op = prog.ops[idx[0]]
+                        if op.wanted_rows and OP_NAMES.get(op.kind) != "linear":
+                            continue
+                        row = kern[key] = {"count": len(idx)}
+                        for phase, ctx_, rows, nreq, dec in (("decode", dctx, B, B, True), ("prefill", pctx, T, 1, False)):
+                            us = time_records(engine, ctx_, idx if len(idx) > 1 else idx * 2)
+                            nbytes, flops = record_cost(op, rows, nreq, pos + 1 if dec else T, dec, page)
+                            row[phase + "_us"] = round(us, 2)
+                            mem_frac = nbytes / (us * 1e-6) / 1e9 / peaks["hbm_gbs"]
+                            peak_f = F32_FMA_TFLOPS if OP_NAMES.get(op.kind) == "linear_attention" else peaks["bf16_tflops"]
+                            flop_frac = flops / (us * 1e-6) / 1e12 / peak_f
+                            row[phase + "_frac"] = round(max(mem_frac, flop_frac), 4)
+                            row[phase + "_bound"] = "memory" if mem_frac >= flop_frac else "compute"
+                    engine.end("kp")
+                for r in ids:
+                    engine.end(r)
+                del engine, weights
+                torch.cuda.empty_cache()
+    out["clocks"] = clocks.summary()
+    print(json.dumps(out))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -254,6 +427,12 @@ def main():
                     help="run a few steps between cudaProfilerStart/Stop (for ncu --profile-from-start off) and exit")
     ap.add_argument("--shape", default="2b", choices=["2b", "1b", "8b"],
                     help="layer sizes: 2b is the headline configuration; the others are for profiles and side measurements")
+    ap.add_argument("--design", default=None, choices=["sitelorn"],
+                    help="instead of the benchmark: prefill and decode of this design at real layer sizes beside the decoder of equal size")
+    ap.add_argument("--design-sizes", default="2k,4k", help="comma-separated names of " + ", ".join(sorted(DESIGN_SIZES)))
+    ap.add_argument("--design-prompt", type=int, default=2048)
+    ap.add_argument("--design-context", type=int, default=2048)
+    ap.add_argument("--design-window", type=int, default=1024)
     ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS),
                     help="instead of the decode benchmark: a serving-style workload through the scheduler")
     args = ap.parse_args()
@@ -270,6 +449,8 @@ def main():
         args.warmup = 3
     if args.workload:
         return run_workload(args.workload, args.layers)
+    if args.design:
+        return run_design(args)
 
     import torch
     from infinicore_infer_b200.config import MiniCPMConfig
