@@ -321,8 +321,8 @@ def run_design(args):
                     cfg = MiniCPMConfig.from_dict(decoder_shape(width, ff, heads, kv_heads, dim, vocab))
                 spec = cfg.model_spec()
                 weights = DeviceRandomWeights(model_manifest(spec), seed=0, compute_dtype=torch.bfloat16, device=dev, std=0.02, untied=True)
-                engine = Engine(spec, weights, dtype=torch.bfloat16, device=dev, cache_tokens=max(B * (context + page), T + 4 * page),
-                                page_size=page, max_requests=B, max_step_tokens=max(T, 256))
+                engine = Engine(spec, weights, dtype=torch.bfloat16, device=dev, cache_tokens=B * (context + page) + T + 4 * page,
+                                page_size=page, max_requests=B + 1, max_step_tokens=max(T, 256))
                 for view in engine.cache.views:
                     if hasattr(view, "k_pages"):
                         view.k_pages.normal_(0, 0.5); view.v_pages.normal_(0, 0.5)
@@ -372,10 +372,7 @@ def run_design(args):
                     pos = engine.cache.length(ids[0])
                     for r in ids:
                         engine.cache.reserve(r, pos + 1)
-                    dctx = engine._upload(entries, [pos] * B, B, B)
-                    engine.begin("kp"); engine.cache.reserve("kp", T)
-                    pctx = engine._upload([StepEntry("kp", ptoks, [T - 1])], [0], 1, T)
-                    names, layer_of, layer = {}, [], -1
+                    names = {}
                     for i in range(prog.count):
                         kind = OP_NAMES.get(prog.ops[i].kind)
                         if kind in ("embed",):
@@ -383,14 +380,15 @@ def run_design(args):
                         op = prog.ops[i]
                         key = f"{kind}:{op.n}x{op.k}" if kind in ("linear", "gate_up", "residual", "qkv") else \
                             (f"{kind}:{'projected' if op.rank else 'constant'}" if kind == "linear_attention" else kind)
-                        names.setdefault(key, []).append(i)
-                    kern = res["records"] = {}
-                    for key, idx in names.items():
-                        op = prog.ops[idx[0]]
-                        if op.wanted_rows and OP_NAMES.get(op.kind) != "linear":
-                            continue
-                        row = kern[key] = {"count": len(idx)}
-                        for phase, ctx_, rows, nreq, dec in (("decode", dctx, B, B, True), ("prefill", pctx, T, 1, False)):
+                        if not (op.wanted_rows and kind != "linear"):
+                            names.setdefault(key, []).append(i)
+                    kern = res["records"] = {key: {"count": len(idx)} for key, idx in names.items()}
+                    engine.begin("kp"); engine.cache.reserve("kp", T)
+                    # one phase after the other: a step's metadata lives in one device buffer, which the next upload rewrites
+                    for phase, rows, nreq, dec in (("decode", B, B, True), ("prefill", T, 1, False)):
+                        ctx_ = engine._upload(entries, [pos] * B, B, B) if dec else engine._upload([StepEntry("kp", ptoks, [T - 1])], [0], 1, T)
+                        for key, idx in names.items():
+                            op, row = prog.ops[idx[0]], kern[key]
                             us = time_records(engine, ctx_, idx if len(idx) > 1 else idx * 2)
                             nbytes, flops = record_cost(op, rows, nreq, pos + 1 if dec else T, dec, page)
                             row[phase + "_us"] = round(us, 2)

@@ -209,7 +209,19 @@ struct DecodeArgs {
     int nrows, nh, nkvh, dh, page_size, max_blocks, window, splits, page_shift;
     float scale_log2;              // softmax scale * log2(e)
     int cluster;                   // 1: the splits of a row are one thread-block cluster and merge among themselves
+    int sink;                      // 1: every softmax has one more key of score 0 that brings no value
+    const float *gate;             // float32 [T, gate_ld]: head h's output is multiplied by sigmoid(gate[t, h]); null: none
+    int gate_ld;
 };
+
+// The factor that turns a row's merged accumulator into its output: 1 / L, where L (relative to the maximum M, in units
+// of log2) takes the sink's term 2^(0 - M) if there is a sink, times the head's gate.
+__device__ __forceinline__ float decode_finish(const DecodeArgs &a, float M, float L, int t, int h) {
+    if (a.sink) L += exp2f(-M);
+    float f = 1.f / L;
+    if (a.gate != nullptr) f *= 1.f / (1.f + expf(-a.gate[(size_t)t * a.gate_ld + h]));
+    return f;
+}
 
 constexpr int DEC_WARPS = 4;
 constexpr int DEC_UNROLL = 4;      // keys a group handles per stage
@@ -402,7 +414,7 @@ attention_decode_kernel(DecodeArgs a) {
         }
         const size_t slot = ((size_t)ri * a.nh + h0 + hh) * a.splits + split;
         if (a.splits == 1) {
-            a.out[((size_t)t * a.nh + h0 + hh) * dh + e] = __float2bfloat16_rn(A / L);
+            a.out[((size_t)t * a.nh + h0 + hh) * dh + e] = __float2bfloat16_rn(A * decode_finish(a, M, L, t, h0 + hh));
         } else {
             a.part_acc[slot * dh + e] = A;
             if (e == 0) { a.part_ml[slot * 2] = M; a.part_ml[slot * 2 + 1] = L; }
@@ -430,7 +442,7 @@ __global__ void attention_combine_kernel(DecodeArgs a) {
             const float ms = a.part_ml[(base + s) * 2];
             if (ms > -INFINITY) A += exp2f(ms - M) * a.part_acc[(base + s) * a.dh + e];
         }
-        a.out[((size_t)t * a.nh + h) * a.dh + e] = __float2bfloat16_rn(A / L);
+        a.out[((size_t)t * a.nh + h) * a.dh + e] = __float2bfloat16_rn(A * decode_finish(a, M, L, t, h));
     }
 }
 
@@ -469,8 +481,9 @@ JK_EXPORT int jk_attention_decode(const void *q, const void *k_pages, const void
                                   float *scratch, const int *rows, int nrows, const int *positions,
                                   const int *row_req, const int *block_table, int max_blocks,
                                   int page_size, int nh, int nkvh, int dh, float scale, int window,
-                                  int splits, cudaStream_t stream) {
+                                  int splits, int sink, const float *gate, int gate_ld, cudaStream_t stream) {
     if (nrows == 0) return JK_OK;
+    JK_REQUIRE(gate == nullptr || gate_ld >= nh, "attention_decode: a gate row of %d holds no %d heads", gate_ld, nh);
     JK_REQUIRE(nrows > 0 && nh > 0 && nkvh > 0 && nh % nkvh == 0, "attention_decode: rows %d heads %d/%d", nrows, nh, nkvh);
     JK_REQUIRE(dh % 8 == 0 && dh >= 8 && dh <= 256, "attention_decode: head size %d (takes multiples of 8 up to 256)", dh);
     JK_REQUIRE(page_size > 0 && max_blocks > 0 && window >= 0, "attention_decode: page size %d, blocks %d, window %d",
@@ -483,7 +496,7 @@ JK_EXPORT int jk_attention_decode(const void *q, const void *k_pages, const void
                  scratch ? scratch + (size_t)nrows * nh * splits * dh : nullptr,
                  rows, positions, row_req, block_table,
                  nrows, nh, nkvh, dh, page_size, max_blocks, window, splits, 0,
-                 scale * 1.4426950408889634f};
+                 scale * 1.4426950408889634f, 0, sink, gate, gate_ld};
     const bool pow2 = (page_size & (page_size - 1)) == 0;
     while ((1 << a.page_shift) < page_size) ++a.page_shift;
     const int g = nh / nkvh;
@@ -530,6 +543,9 @@ struct PrefillArgs {
     const int *block_table;  // [nreq, max_blocks]
     int ntiles, nh, nkvh, page_size, max_blocks, window, tile_rows;
     float scale_log2;
+    int sink;                // 1: every softmax has one more key of score 0 that brings no value
+    const float *gate;       // float32 [T, gate_ld]: head h's output is multiplied by sigmoid(gate[t, h]); null: none
+    int gate_ld;
 };
 
 constexpr int PF_BM = 64;
@@ -706,7 +722,15 @@ attention_prefill_kernel(PrefillArgs a) {
     }
     l_a += __shfl_xor_sync(0xffffffffu, l_a, 1); l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
     l_b += __shfl_xor_sync(0xffffffffu, l_b, 1); l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
-    const float inv_a = 1.f / l_a, inv_b = 1.f / l_b;
+    if (a.sink) {       // the sink's term relative to each row's maximum (raw scores; the exponent is scaled)
+        l_a += exp2f(-m_a * a.scale_log2);
+        l_b += exp2f(-m_b * a.scale_log2);
+    }
+    float inv_a = 1.f / l_a, inv_b = 1.f / l_b;
+    if (a.gate != nullptr) {
+        if (row_a < nrows) inv_a *= 1.f / (1.f + expf(-a.gate[(size_t)(row0 + row_a) * a.gate_ld + h]));
+        if (row_b < nrows) inv_b *= 1.f / (1.f + expf(-a.gate[(size_t)(row0 + row_b) * a.gate_ld + h]));
+    }
 #pragma unroll
     for (int i = 0; i < DH / 8; ++i) {
         const int col = i * 8 + 2 * (lane & 3);
@@ -1000,7 +1024,7 @@ attention_decode_gqa_kernel(DecodeArgs a) {
             fin[r * DH + e] = A;
             if (e == 0) { fin_ml[2 * r] = M; fin_ml[2 * r + 1] = L; }
         } else if (a.splits == 1) {
-            a.out[((size_t)t * a.nh + h0 + r) * DH + e] = __float2bfloat16_rn(A / L);
+            a.out[((size_t)t * a.nh + h0 + r) * DH + e] = __float2bfloat16_rn(A * decode_finish(a, M, L, t, h0 + r));
         } else {
             const size_t slot = pbase + (size_t)r * a.splits;
             a.part_acc[slot * DH + e] = A;
@@ -1025,7 +1049,7 @@ attention_decode_gqa_kernel(DecodeArgs a) {
                         A += f * ld_cluster_f32(fin + idx, p);
                     }
                 }
-                a.out[((size_t)t * a.nh + h0 + r) * DH + (idx % DH)] = __float2bfloat16_rn(A / L);
+                a.out[((size_t)t * a.nh + h0 + r) * DH + (idx % DH)] = __float2bfloat16_rn(A * decode_finish(a, M, L, t, h0 + r));
             }
         }
         cluster_sync_all();                        // nobody leaves while its shared memory may still be read
@@ -1107,15 +1131,16 @@ JK_EXPORT int jk_attention_prefill_supports(int dh) {
 JK_EXPORT int jk_attention_prefill(const void *q, const void *k_pages, const void *v_pages, void *out,
                                    const int *tiles, int ntiles, int tile_rows, const int *req_start, const int *req_pos,
                                    const int *block_table, int max_blocks, int page_size, int nh, int nkvh,
-                                   int dh, float scale, int window, cudaStream_t stream) {
+                                   int dh, float scale, int window, int sink, const float *gate, int gate_ld, cudaStream_t stream) {
     if (ntiles == 0) return JK_OK;
     JK_REQUIRE(ntiles > 0 && nh > 0 && nkvh > 0 && nh % nkvh == 0, "attention_prefill: tiles %d heads %d/%d", ntiles, nh, nkvh);
+    JK_REQUIRE(gate == nullptr || gate_ld >= nh, "attention_prefill: a gate row of %d holds no %d heads", gate_ld, nh);
     JK_REQUIRE(ntiles * (tile_rows / PF_BM) <= 65535, "attention_prefill: %d tiles exceed one launch", ntiles);
     JK_REQUIRE(page_size > 0 && max_blocks > 0 && window >= 0, "attention_prefill: page size %d, blocks %d, window %d",
                page_size, max_blocks, window);
     PrefillArgs a{(const __nv_bfloat16 *)q, (const __nv_bfloat16 *)k_pages, (const __nv_bfloat16 *)v_pages,
                   (__nv_bfloat16 *)out, tiles, req_start, req_pos, block_table,
-                  ntiles, nh, nkvh, page_size, max_blocks, window, tile_rows, scale * 1.4426950408889634f};
+                  ntiles, nh, nkvh, page_size, max_blocks, window, tile_rows, scale * 1.4426950408889634f, sink, gate, gate_ld};
     JK_REQUIRE(tile_rows >= PF_BM && tile_rows % PF_BM == 0, "attention_prefill: tiles of %d rows (a multiple of %d is needed)", tile_rows, PF_BM);
     switch (dh) {
         case 16: return launch_prefill<16, 64>(a, stream);
@@ -1182,5 +1207,5 @@ JK_EXPORT int jk_attention_decode_static(const void *q, const void *k_pages, con
     // every partial slot that the merge kernel reads is written by the split kernel of this same call,
     // so what an earlier call left in the array needs no clearing
     return jk_attention_decode(q, k_pages, v_pages, out, need ? scratch : nullptr, rows, nrows, positions, row_req,
-                               block_table, max_blocks, page_size, nh, nkvh, dh, scale, window, splits, stream);
+                               block_table, max_blocks, page_size, nh, nkvh, dh, scale, window, splits, 0, nullptr, 0, stream);
 }

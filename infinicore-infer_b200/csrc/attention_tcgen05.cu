@@ -59,6 +59,9 @@ struct AtArgs {
     int *status;
     int ntiles, nh, nkvh, page_size, max_blocks, window;
     float scale_log2;
+    int sink;                 // 1: every softmax has one more key of score 0 that brings no value
+    const float *gate;        // float32 [T, gate_ld]: head h's output is multiplied by sigmoid(gate[t, h]); null: none
+    int gate_ld;
 };
 
 // ---- PTX wrappers (see gemm_tcgen05.cu for the same set) -----------------------------------------
@@ -483,7 +486,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             // a half that saw no key has reference -inf, sum 0 and an accumulator of zeros
             const float m_all = fmaxf(m_ref, other.x);
             const float w_mine = ex2(m_ref - m_all), w_other = ex2(other.x - m_all);
-            const float inv = 1.f / (l * w_mine + other.y * w_other);
+            // a sink adds its term 2^(0 - m_all); a gate multiplies the row's output
+            float inv = 1.f / (l * w_mine + other.y * w_other + (a.sink ? exp2f(-m_all) : 0.f));
+            if (a.gate != nullptr && row < nrows) inv *= 1.f / (1.f + expf(-a.gate[(size_t)(row0 + row) * a.gate_ld + h]));
             const float w0 = (half ? w_other : w_mine) * inv, w1 = (half ? w_mine : w_other) * inv;
             // this thread writes columns [half * DH / 2, + DH / 2) of its row
             __nv_bfloat16 *dst = a.out + ((size_t)(row0 + row) * a.nh + h) * DH + half * (DH / 2);
@@ -582,8 +587,9 @@ static int launch_at(const CUtensorMap &mq, const CUtensorMap &mk, const CUtenso
 JK_EXPORT int jk_attention_tcgen05(const void *q, const void *k_pages, const void *v_pages, void *out, const int *tiles,
                                    int ntiles, int ntok, const int *req_start, const int *req_pos, const int *block_table,
                                    int max_blocks, int num_pages, int page_size, int nh, int nkvh, int dh, float scale,
-                                   int window, int *status, cudaStream_t stream) {
+                                   int window, int *status, int sink, const float *gate, int gate_ld, cudaStream_t stream) {
     if (ntiles == 0) return JK_OK;
+    JK_REQUIRE(gate == nullptr || gate_ld >= nh, "attention_tcgen05: a gate row of %d holds no %d heads", gate_ld, nh);
     JK_REQUIRE(jk_attention_tcgen05_supports(dh, page_size), "attention_tcgen05: head size %d with pages of %d is not built", dh, page_size);
     JK_REQUIRE(ntiles > 0 && nh > 0 && nkvh > 0 && nh % nkvh == 0 && ntiles <= 65535, "attention_tcgen05: tiles %d heads %d/%d", ntiles, nh, nkvh);
     JK_REQUIRE(max_blocks > 0 && window >= 0 && status != nullptr && num_pages > 0, "attention_tcgen05: bad arguments");
@@ -592,7 +598,7 @@ JK_EXPORT int jk_attention_tcgen05(const void *q, const void *k_pages, const voi
     if (int rc = tensor_map(k_pages, (long long)num_pages * nkvh * page_size, dh, page_size, &mk)) return rc;
     if (int rc = tensor_map(v_pages, (long long)num_pages * nkvh * page_size, dh, page_size, &mv)) return rc;
     AtArgs a{(__nv_bfloat16 *)out, tiles, req_start, req_pos, block_table, status,
-             ntiles, nh, nkvh, page_size, max_blocks, window, scale * 1.4426950408889634f};
+             ntiles, nh, nkvh, page_size, max_blocks, window, scale * 1.4426950408889634f, sink, gate, gate_ld};
     if (dh == 64) return launch_at<64>(mq, mk, mv, a, stream);
     return launch_at<128>(mq, mk, mv, a, stream);
 }

@@ -331,9 +331,12 @@ JK_EXPORT int jk_conv_qkv(const float *u, int ld, int q_off, int k_off, int v_of
 // q, k, v pass `qkv_act` (none or silu); q is multiplied by q_scale.  The decay a_t [dk] is either one constant per head
 // (decay[head], for all channels and rows) or projected: z = W2 r_t + b2 with r_t the `rank` columns of the fused
 // product at r_off, a = exp(log_sigmoid(z) / tau), all in float32 (W2 may be stored as bfloat16).
-// A block owns (head, request, a slice of `cols` value columns) and walks the request's rows in order; its threads are
-// (key group, column): thread (g, v) keeps S[g-th slice of dk][v] in registers.  Rows of a step beyond one per request
-// cost a barrier each; the state is read and written once per step.
+// A block owns (head, request, a slice of value columns) and walks the request's rows in order.  Its 128 threads are
+// (column, part): `kq` neighbouring lanes share a column of S, lane `part` keeping the key channels part, part + kq,
+// part + 2 kq ... in registers; a row's output is the lanes' partial sums added by shuffles.  Rows are staged through
+// shared memory a chunk at a time (activations applied, decays formed there, once per block), so a row costs no block
+// barrier; the state is read and written once per step.  The order of every sum is fixed by the shape alone: a row's
+// output does not depend on how the sequence was cut into steps or on what else the step holds.
 // ---------------------------------------------------------------------------------------------------------------
 struct ScanArgs {
     const float *u;             // [T, ld]
@@ -341,14 +344,15 @@ struct ScanArgs {
     int heads, dk, dv, qkv_act;
     float q_scale;
     const float *decay;         // [heads] or null
-    const void *w2;             // [heads * dk, rank] (W2T: float or bfloat16) or null
+    const void *w2;             // [heads * dk, rank] (TW: float or bfloat16) or null
     const float *b2;            // [heads * dk] or null
     int rank;
     float inv_tau;
     float *state;               // [slots, heads, dk, dv]
     const int *req_start, *slot_ids;
     float *out;                 // [T, heads * dv] float32
-    int cols;                   // value columns per block
+    int kq;                     // lanes that share a column (a power of two up to 32)
+    int chunk;                  // rows staged at a time
 };
 
 constexpr int SCAN_THREADS = 128;
@@ -359,63 +363,63 @@ linear_scan_kernel(ScanArgs a) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ __align__(16) float sm[];
-    const int head = blockIdx.x, req = blockIdx.y, c0 = blockIdx.z * a.cols;
-    const int cols = min(a.cols, a.dv - c0);
-    const int groups = SCAN_THREADS / a.cols;           // key groups: groups * KS >= dk
-    float *sq = sm;                                     // [dk]
-    float *sk = sq + a.dk;                              // [dk]
-    float *sa = sk + a.dk;                              // [dk]
-    float *sv = sa + a.dk;                              // [cols]
-    float *part = sv + a.cols;                          // [groups, cols]
-    const int g = threadIdx.x / a.cols, v = threadIdx.x % a.cols;
-    const bool owner = g < groups && v < cols;
-    const int k0 = g * KS;
+    const int kq = a.kq, cols = SCAN_THREADS / kq, dk = a.dk;
+    const int head = blockIdx.x, req = blockIdx.y, c0 = blockIdx.z * cols;
+    float *sq = sm;                                     // [chunk, dk]
+    float *sk = sq + (size_t)a.chunk * dk;              // [chunk, dk]
+    float *sa = sk + (size_t)a.chunk * dk;              // [chunk, dk]
+    float *sv = sa + (size_t)a.chunk * dk;              // [chunk, cols]
+    const int col = threadIdx.x / kq, part = threadIdx.x % kq;
+    const bool live = c0 + col < a.dv;
     const int first = a.req_start[req], last = a.req_start[req + 1];
-    float *S = a.state + (((size_t)a.slot_ids[req] * a.heads + head) * a.dk) * a.dv + c0;
+    float *S = a.state + (((size_t)a.slot_ids[req] * a.heads + head) * dk) * a.dv + c0 + col;
     float s[KS];
 #pragma unroll
-    for (int i = 0; i < KS; ++i) s[i] = (owner && k0 + i < a.dk) ? S[(size_t)(k0 + i) * a.dv + v] : 0.f;
+    for (int i = 0; i < KS; ++i) s[i] = (live && part + i * kq < dk) ? S[(size_t)(part + i * kq) * a.dv] : 0.f;
     const float head_decay = a.decay ? a.decay[head] : 1.f;
-    for (int t = first; t < last; ++t) {
-        const float *row = a.u + (size_t)t * a.ld;
-        __syncthreads();            // the row before is done with sq / sk / sa / sv / part
-        for (int i = threadIdx.x; i < a.dk; i += SCAN_THREADS) {
-            sq[i] = apply_act(a.qkv_act, row[a.q_off + head * a.dk + i]) * a.q_scale;
-            sk[i] = apply_act(a.qkv_act, row[a.k_off + head * a.dk + i]);
+    for (int t0 = first; t0 < last; t0 += a.chunk) {
+        const int n = min(a.chunk, last - t0);
+        __syncthreads();            // the chunk before has been read
+        for (int i = threadIdx.x; i < n * dk; i += SCAN_THREADS) {
+            const int tt = i / dk, kk = i - tt * dk;
+            const float *row = a.u + (size_t)(t0 + tt) * a.ld;
+            sq[i] = apply_act(a.qkv_act, row[a.q_off + head * dk + kk]) * a.q_scale;
+            sk[i] = apply_act(a.qkv_act, row[a.k_off + head * dk + kk]);
             float dec = head_decay;
             if (a.w2 != nullptr) {
-                const TW *w = (const TW *)a.w2 + (size_t)(head * a.dk + i) * a.rank;
-                float z = a.b2 ? a.b2[head * a.dk + i] : 0.f;
+                const TW *w = (const TW *)a.w2 + (size_t)(head * dk + kk) * a.rank;
+                float z = a.b2 ? a.b2[head * dk + kk] : 0.f;
                 for (int r = 0; r < a.rank; ++r) z = fmaf(to_f32(w[r]), row[a.r_off + r], z);
                 dec = expf(log_sigmoid_f(z) * a.inv_tau);
             }
             sa[i] = dec;
         }
-        for (int i = threadIdx.x; i < cols; i += SCAN_THREADS) sv[i] = apply_act(a.qkv_act, row[a.v_off + head * a.dv + c0 + i]);
+        for (int i = threadIdx.x; i < n * cols; i += SCAN_THREADS) {
+            const int tt = i / cols, cc = i - tt * cols;
+            sv[i] = c0 + cc < a.dv ? apply_act(a.qkv_act, a.u[(size_t)(t0 + tt) * a.ld + a.v_off + head * a.dv + c0 + cc]) : 0.f;
+        }
         __syncthreads();
-        float o = 0.f;
-        if (owner) {
-            const float vv = sv[v];
+        for (int tt = 0; tt < n; ++tt) {
+            const float vv = sv[tt * cols + col];
+            const float *q = sq + (size_t)tt * dk + part, *k = sk + (size_t)tt * dk + part, *al = sa + (size_t)tt * dk + part;
+            float o0 = 0.f, o1 = 0.f;
 #pragma unroll
             for (int i = 0; i < KS; ++i) {
-                if (k0 + i < a.dk) {
-                    s[i] = fmaf(sa[k0 + i], s[i], sk[k0 + i] * vv);
-                    o = fmaf(s[i], sq[k0 + i], o);
+                if (part + i * kq < dk) {
+                    s[i] = fmaf(al[i * kq], s[i], k[i * kq] * vv);
+                    if (i & 1) o1 = fmaf(s[i], q[i * kq], o1);
+                    else o0 = fmaf(s[i], q[i * kq], o0);
                 }
             }
-            part[g * a.cols + v] = o;
-        }
-        __syncthreads();
-        if (threadIdx.x < cols) {
-            float sum = 0.f;
-            for (int gg = 0; gg < groups; ++gg) sum += part[gg * a.cols + threadIdx.x];
-            a.out[(size_t)t * a.heads * a.dv + head * a.dv + c0 + threadIdx.x] = sum;
+            float o = o0 + o1;
+            for (int off = kq >> 1; off > 0; off >>= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
+            if (part == 0 && live) a.out[(size_t)(t0 + tt) * a.heads * a.dv + head * a.dv + c0 + col] = o;
         }
     }
-    if (owner) {
+    if (live) {
 #pragma unroll
         for (int i = 0; i < KS; ++i)
-            if (k0 + i < a.dk) S[(size_t)(k0 + i) * a.dv + v] = s[i];
+            if (part + i * kq < dk) S[(size_t)(part + i * kq) * a.dv] = s[i];
     }
 }
 
@@ -427,22 +431,25 @@ JK_EXPORT int jk_linear_scan(const float *u, int ld, int q_off, int k_off, int v
     JK_REQUIRE(u && state && req_start && slot_ids && out && heads > 0 && dk > 0 && dv > 0, "linear_scan: an argument is missing");
     JK_REQUIRE((decay != nullptr) != (w2 != nullptr), "linear_scan: the decay is a constant per head or projected, one of the two");
     JK_REQUIRE(w2 == nullptr || (rank > 0 && tau > 0.f), "linear_scan: a projected decay of rank %d, tau %g", rank, tau);
-    JK_REQUIRE(dk <= 1024, "linear_scan: %d key channels a head exceed 1024", dk);
-    // columns per block: a power of two up to 128; fewer columns make more blocks (a decode step of few requests should
-    // still reach every SM) and more key groups a block, as long as a thread keeps at most 64 channels
-    int cols = 1;
-    while (cols < dv && cols < SCAN_THREADS) cols *= 2;
+    JK_REQUIRE(dk <= 2048, "linear_scan: %d key channels a head exceed 2048", dk);
+    // lanes per column: as few as keep a thread's share of a column at 32 channels (64 beyond 1024 channels); more of them,
+    // and so fewer columns a block and more blocks, while the blocks do not fill the SMs
     const int sm_count = sms > 0 ? sms : 148;
-    while (cols > 8 && (long long)heads * nreq * ((dv + cols - 1) / cols) < 2LL * sm_count) cols /= 2;
-    while ((dk + SCAN_THREADS / cols - 1) / (SCAN_THREADS / cols) > 64) cols /= 2;
-    JK_REQUIRE(cols >= 1, "linear_scan: no way to cut %d x %d", dk, dv);
-    const int groups = SCAN_THREADS / cols;
-    const int per_thread = (dk + groups - 1) / groups;
+    int kq = 1;
+    while (kq < 32 && (dk + kq - 1) / kq > 32) kq *= 2;
+    while (kq < 32 && (dk + 2 * kq - 1) / (2 * kq) >= 1 && 2 * kq <= dk &&
+           (long long)heads * nreq * ((dv + SCAN_THREADS / kq - 1) / (SCAN_THREADS / kq)) < sm_count)
+        kq *= 2;
+    const int cols = SCAN_THREADS / kq;
+    const int per_thread = (dk + kq - 1) / kq;
+    const size_t row_bytes = sizeof(float) * (3 * (size_t)dk + cols);
+    int chunk = (int)std::min<size_t>(32, std::max<size_t>(1, (40 * 1024) / row_bytes));
+    chunk = std::min(chunk, T);
     ScanArgs a{u, ld, q_off, k_off, v_off, r_off, heads, dk, dv, qkv_act, q_scale, decay, w2, b2, rank, tau > 0.f ? 1.f / tau : 0.f,
-               state, req_start, slot_ids, out, cols};
+               state, req_start, slot_ids, out, kq, chunk};
     dim3 grid(heads, nreq, (dv + cols - 1) / cols);
     JK_REQUIRE(nreq <= 65535 && grid.z <= 65535, "linear_scan: %d requests in one launch", nreq);
-    const size_t smem = sizeof(float) * (3 * (size_t)dk + cols + (size_t)groups * cols);
+    const size_t smem = row_bytes * chunk;
 #define SCAN_LAUNCH(TW, KS) jk_launch(linear_scan_kernel<TW, KS>, grid, dim3(SCAN_THREADS), smem, stream, a)
 #define SCAN_LAUNCH_T(TW)                                   \
     do {                                                    \

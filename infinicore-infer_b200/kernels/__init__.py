@@ -418,6 +418,16 @@ def _sm_count(device) -> int:
     return _SMS[key]
 
 
+def _gate_args(gate: Optional[torch.Tensor], rows: int, nh: int):
+    """(pointer, leading dimension) of a float32 gate ``[rows, >= nh]`` (a view of wider rows is fine), or nulls."""
+    if gate is None:
+        return _ptr(None), _c_int(0)
+    _need(gate, "gate", torch.float32, contiguous=False)
+    if gate.dim() != 2 or gate.stride(1) != 1 or gate.shape[0] < rows or gate.shape[1] < nh:
+        raise KernelError("attention: gate must be [rows, heads] with unit stride along heads")
+    return _ptr(gate), _c_int(gate.stride(0))
+
+
 def attention_rows(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor,
                    positions: torch.Tensor, row_req: torch.Tensor, block_table: torch.Tensor, ntok: int,
                    nh: int, scale: float, window: int = 0, sink: bool = False,
@@ -453,7 +463,7 @@ def attention_rows(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor
 def attention_decode(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor,
                      rows: Optional[torch.Tensor], nrows: int, positions: torch.Tensor, row_req: torch.Tensor,
                      block_table: torch.Tensor, nh: int, scale: float, window: int, splits: int,
-                     scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
+                     scratch: Optional[torch.Tensor] = None, sink: bool = False, gate: Optional[torch.Tensor] = None) -> torch.Tensor:
     """bfloat16 attention of rows that bring few queries per request (decoded tokens, short portions):
     the key range of every (row, key/value head) is cut into ``splits`` blocks whose partial results
     a second kernel merges.  ``rows`` lists the rows to work on (None: rows 0..nrows-1)."""
@@ -476,7 +486,8 @@ def attention_decode(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tens
     _check("attention", lib.jk_attention_decode(
         _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(scratch if need else None), _ptr(rows), _c_int(nrows),
         _ptr(positions), _ptr(row_req), _ptr(block_table), _c_int(block_table.shape[1]), _c_int(page_size),
-        _c_int(nh), _c_int(nkvh), _c_int(dh), _c_float(scale), _c_int(window or 0), _c_int(splits), _stream()))
+        _c_int(nh), _c_int(nkvh), _c_int(dh), _c_float(scale), _c_int(window or 0), _c_int(splits), _c_int(1 if sink else 0),
+        *_gate_args(gate, 0, nh), _stream()))
     if need and splits > 1:
         global launch_count
         launch_count += 1          # the merge kernel
@@ -492,7 +503,8 @@ TILE_ROWS = _host.attention_tile_rows()      # rows of a query tile in the tile 
 
 def attention_prefill(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor,
                       tiles: torch.Tensor, ntiles: int, req_start: torch.Tensor, req_pos: torch.Tensor,
-                      block_table: torch.Tensor, nh: int, scale: float, window: int = 0) -> torch.Tensor:
+                      block_table: torch.Tensor, nh: int, scale: float, window: int = 0, sink: bool = False,
+                      gate: Optional[torch.Tensor] = None) -> torch.Tensor:
     """bfloat16 tensor-core (mma.sync) attention of requests that bring many rows: ``tiles[i] = (batch
     entry, first row)`` names TILE_ROWS-row tiles of query rows."""
     for name, t in (("q", q), ("k_pages", k_pages), ("v_pages", v_pages), ("out", out)):
@@ -506,7 +518,7 @@ def attention_prefill(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Ten
     _check("attention", lib.jk_attention_prefill(
         _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(tiles), _c_int(ntiles), _c_int(TILE_ROWS), _ptr(req_start),
         _ptr(req_pos), _ptr(block_table), _c_int(block_table.shape[1]), _c_int(page_size), _c_int(nh), _c_int(nkvh),
-        _c_int(dh), _c_float(scale), _c_int(window or 0), _stream()))
+        _c_int(dh), _c_float(scale), _c_int(window or 0), _c_int(1 if sink else 0), *_gate_args(gate, 0, nh), _stream()))
     return out
 
 
@@ -518,7 +530,8 @@ def attention_tcgen05_supports(dh: int, page_size: int) -> bool:
 
 def attention_tcgen05(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor,
                       tiles: torch.Tensor, ntiles: int, ntok: int, req_start: torch.Tensor, req_pos: torch.Tensor,
-                      block_table: torch.Tensor, nh: int, scale: float, window: int = 0) -> torch.Tensor:
+                      block_table: torch.Tensor, nh: int, scale: float, window: int = 0, sink: bool = False,
+                      gate: Optional[torch.Tensor] = None) -> torch.Tensor:
     """The same attention of TILE_ROWS-row query tiles on the tcgen05 tensor cores (TMA operands, both
     products with accumulators in tensor memory); head sizes 64 and 128, pages that divide 128."""
     for name, t in (("q", q), ("k_pages", k_pages), ("v_pages", v_pages), ("out", out)):
@@ -532,7 +545,8 @@ def attention_tcgen05(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Ten
     _check("attention_tcgen05", lib.jk_attention_tcgen05(
         _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(tiles), _c_int(ntiles), _c_int(ntok), _ptr(req_start),
         _ptr(req_pos), _ptr(block_table), _c_int(block_table.shape[1]), _c_int(num_pages), _c_int(page_size), _c_int(nh),
-        _c_int(nkvh), _c_int(dh), _c_float(scale), _c_int(window or 0), _ptr(gemm_status(q.device)), _stream()))
+        _c_int(nkvh), _c_int(dh), _c_float(scale), _c_int(window or 0), _ptr(gemm_status(q.device)), _c_int(1 if sink else 0),
+        *_gate_args(gate, ntok, nh), _stream()))
     return out
 
 

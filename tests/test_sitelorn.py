@@ -55,6 +55,12 @@ MODELS = {
     "mixed-b": config(64, 130, [lightning(1, 40, 72, [0.98], ff=48), attention(2, 2, 16, 16, 1, 16, 1e3, 0.5, 5, ff=48),
                                 lightning(4, 8, 8, [0.3, 0.8, 0.99, 1.0]), attention(3, 3, 20, 12, 5, 0, 1e4, 0.45, 64, ff=96)],
                        scale=1.0, eps=3e-6),
+    # head sizes that the tensor-core attention kernels take (64 and 128: tcgen05 tiles and the grouped decode kernel; 32: the
+    # mma.sync tiles and the per-head decode kernel), keys and values of one size
+    "heads64": config(128, 140, [attention(4, 2, 64, 64, 3, 32, 1e4, 0.2, 70, ff=96), gla(2, 64, 64, 4.0, 8),
+                                 attention(4, 2, 64, 64, 2, 32, 1e4, 0.15, 131, kv_from=0, ff=96)], scale=2.0),
+    "heads128": config(128, 99, [attention(2, 1, 128, 128, 4, 64, 5e5, 0.12, 40, ff=64), lightning(2, 128, 128, [0.9, 0.999], ff=64)]),
+    "heads32": config(64, 77, [attention(6, 2, 32, 32, 2, 8, 1e4, 0.3, 23, ff=64), attention(6, 2, 32, 32, 3, 8, 1e4, 0.3, 11, kv_from=0)]),
 }
 STD = 0.16     # matrices N(0, STD): products keep their input's spread, so scores and gates are far from flat
 
@@ -137,6 +143,17 @@ def test_whole_tail_and_portions_agree_with_the_plain_implementation(folders, en
                             ("uneven", portions("r", toks, sizes=(17, 3, 31, 2, 16)))):
             check(run(eng, steps), "r", want, TOL[dtype], f"{name} {dtype} {what} n={n}")
         eng.cache.check_invariants()
+
+
+def test_sink_and_gate_in_the_legacy_tensor_core_tiles(folders):
+    """The mma.sync prefill tiles (what runs where the tcgen05 kernel is not built) with heads of 64."""
+    from infinicore_infer_b200.engine import Engine
+    eng = Engine.from_folder(folders["heads64"][0], dtype=torch.bfloat16, max_tokens=512, cache_tokens=512, page_size=16,
+                             max_requests=2, max_step_tokens=512)
+    eng.runtime.legacy_tensor_cores = True
+    toks, want = expected(folders, "heads64", 302, 150)
+    for what, steps in (("whole", whole("r", toks)), ("uneven", portions("r", toks, sizes=(17, 3, 31, 2, 16)))):
+        check(run(eng, steps), "r", want, TOL["bfloat16"], f"legacy tiles {what}")
 
 
 @pytest.mark.parametrize("dtype", list(DTYPES))
