@@ -43,6 +43,8 @@ JK_HOST_EXPORT int jk_pack_step(int *host, int T_padded, int B, int pad_B, int e
 // ---- the attention mixer's work lists ---------------------------------------------------------------------------
 JK_HOST_EXPORT int jk_attention_short_rows() { return jk::SHORT_ROWS; }
 JK_HOST_EXPORT int jk_attention_tile_rows() { return jk::TILE_ROWS; }
+JK_HOST_EXPORT int jk_scan_piece() { return jk::SCAN_PIECE; }
+JK_HOST_EXPORT long long jk_scan_max_pieces(long long rows) { return jk::scan_max_pieces(rows); }
 JK_HOST_EXPORT int jk_attention_short_rows_capacity(int T) { return jk::attention_short_rows_capacity(T); }
 JK_HOST_EXPORT int jk_attention_tiles_capacity(int T, int B) { return jk::attention_tiles_capacity(T, B); }
 // counts[0..1]: short rows, tiles

@@ -171,6 +171,16 @@ inline AttentionLists attention_work_lists(int B, int pad_B, const int *lens, co
     return c;
 }
 
+// ---- the pieces of a linear-attention recurrence -------------------------------------------------------------------
+// A request that brings more than SCAN_PIECE rows to a step has its recurrence cut into pieces of that many rows, which
+// run side by side and are then joined (csrc/mixers.cu); the others run from their state slot in one go.  A step of
+// `rows` rows has at most scan_max_pieces(rows) pieces.
+constexpr int SCAN_PIECE = 64;
+inline long long scan_max_pieces(long long rows) { return 2 * rows / SCAN_PIECE + 1; }
+inline long long scan_scratch_floats(long long rows, int heads, int dk, int dv, bool projected) {
+    return scan_max_pieces(rows) * heads * dk * dv + (projected ? rows * heads * dk : 0);
+}
+
 // ---- how many ways the decode attention cuts each row's key range ------------------------------------------------
 // It depends on the batch's size and on `keys`, the context length the step is planned for (a captured step keeps
 // its grid, so the caller passes a bucket of the live lengths, not the lengths themselves).

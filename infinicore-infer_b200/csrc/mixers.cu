@@ -12,6 +12,7 @@
 // state reads what earlier steps left and leaves what later steps need, so a whole prompt, a portion and a single token
 // are one case.
 #include "common.cuh"
+#include "host_rules.h"
 
 #include <algorithm>
 
@@ -331,13 +332,23 @@ JK_EXPORT int jk_conv_qkv(const float *u, int ld, int q_off, int k_off, int v_of
 // q, k, v pass `qkv_act` (none or silu); q is multiplied by q_scale.  The decay a_t [dk] is either one constant per head
 // (decay[head], for all channels and rows) or projected: z = W2 r_t + b2 with r_t the `rank` columns of the fused
 // product at r_off, a = exp(log_sigmoid(z) / tau), all in float32 (W2 may be stored as bfloat16).
-// A block owns (head, request, a slice of value columns) and walks the request's rows in order.  Its 128 threads are
-// (column, part): `kq` neighbouring lanes share a column of S, lane `part` keeping the key channels part, part + kq,
-// part + 2 kq ... in registers; a row's output is the lanes' partial sums added by shuffles.  Rows are staged through
-// shared memory a chunk at a time (activations applied, decays formed there, once per block), so a row costs no block
-// barrier; the state is read and written once per step.  The order of every sum is fixed by the shape alone: a row's
-// output does not depend on how the sequence was cut into steps or on what else the step holds.
+// A block of the scan kernel owns (head, work item, a slice of value columns) and walks the item's rows in order.  Its 128
+// threads are (column, part): `kq` neighbouring lanes share a column of S, lane `part` keeping the key channels part,
+// part + kq, part + 2 kq ... in registers; a row's output is the lanes' partial sums added by shuffles.  Rows are staged
+// through shared memory a chunk at a time (activations applied, decays formed there, once per block), so a row costs no
+// block barrier; the state is read and written once per item.
+//
+// Work items.  A request that brings at most SCAN_PIECE rows is one item: from its state slot, through its rows, back into
+// the slot ("direct").  A longer portion is cut into pieces of SCAN_PIECE rows that run side by side, each from a state of
+// zeros: a piece leaves its rows' outputs without what came before the piece, its own end state in `piece_state`, and (for
+// a projected decay) the running product of the decays since the piece's start, b_t, in `cum`.  `scan_carry_kernel` then
+// walks each such request's pieces in order, S <- diag(b_end) S + S_piece, leaving in `piece_state` the state at each piece's
+// START and in the slot the state after the last; `scan_prefix_kernel` adds (q_t * b_t)^T S_start to the piece's rows.
+// Nothing is ever divided by a decay.  The order of the sums of a row depends on where its piece starts (every SCAN_PIECE
+// rows from the start of its portion) and on nothing else of the batch.
 // ---------------------------------------------------------------------------------------------------------------
+constexpr int SCAN_PIECE = jk::SCAN_PIECE;
+
 struct ScanArgs {
     const float *u;             // [T, ld]
     int ld, q_off, k_off, v_off, r_off;
@@ -353,6 +364,13 @@ struct ScanArgs {
     float *out;                 // [T, heads * dv] float32
     int kq;                     // lanes that share a column (a power of two up to 32)
     int chunk;                  // rows staged at a time
+    const int *direct;          // [n_direct] requests that run as one item (null: requests 0 .. n_direct-1)
+    int n_direct;
+    const int *pieces;          // [n_pieces, 2] (first row, rows)
+    int n_pieces;
+    const int *piece_reqs;      // [n_piece_reqs, 3] (request, its first piece, its pieces)
+    float *piece_state;         // [n_pieces, heads, dk, dv]
+    float *cum;                 // [T, heads, dk] running products of a projected decay inside each piece
 };
 
 constexpr int SCAN_THREADS = 128;
@@ -364,41 +382,87 @@ linear_scan_kernel(ScanArgs a) {
     pdl_wait();
     extern __shared__ __align__(16) float sm[];
     const int kq = a.kq, cols = SCAN_THREADS / kq, dk = a.dk;
-    const int head = blockIdx.x, req = blockIdx.y, c0 = blockIdx.z * cols;
+    const int head = blockIdx.x, item = blockIdx.y, c0 = blockIdx.z * cols;
     float *sq = sm;                                     // [chunk, dk]
     float *sk = sq + (size_t)a.chunk * dk;              // [chunk, dk]
     float *sa = sk + (size_t)a.chunk * dk;              // [chunk, dk]
     float *sv = sa + (size_t)a.chunk * dk;              // [chunk, cols]
+    float *sr = sv + (size_t)a.chunk * cols;            // [chunk, rank]
     const int col = threadIdx.x / kq, part = threadIdx.x % kq;
     const bool live = c0 + col < a.dv;
-    const int first = a.req_start[req], last = a.req_start[req + 1];
-    float *S = a.state + (((size_t)a.slot_ids[req] * a.heads + head) * dk) * a.dv + c0 + col;
+    int first, last;
+    float *S;
+    const bool piece = item >= a.n_direct;
+    if (!piece) {
+        const int req = a.direct ? a.direct[item] : item;
+        first = a.req_start[req]; last = a.req_start[req + 1];
+        S = a.state + (((size_t)a.slot_ids[req] * a.heads + head) * dk) * a.dv + c0 + col;
+    } else {
+        const int p = item - a.n_direct;
+        first = a.pieces[2 * p]; last = first + a.pieces[2 * p + 1];
+        S = a.piece_state + (((size_t)p * a.heads + head) * dk) * a.dv + c0 + col;
+    }
     float s[KS];
 #pragma unroll
-    for (int i = 0; i < KS; ++i) s[i] = (live && part + i * kq < dk) ? S[(size_t)(part + i * kq) * a.dv] : 0.f;
+    for (int i = 0; i < KS; ++i) s[i] = (!piece && live && part + i * kq < dk) ? S[(size_t)(part + i * kq) * a.dv] : 0.f;
     const float head_decay = a.decay ? a.decay[head] : 1.f;
+    const bool write_cum = piece && a.w2 != nullptr && blockIdx.z == 0;
     for (int t0 = first; t0 < last; t0 += a.chunk) {
         const int n = min(a.chunk, last - t0);
         __syncthreads();            // the chunk before has been read
-        for (int i = threadIdx.x; i < n * dk; i += SCAN_THREADS) {
-            const int tt = i / dk, kk = i - tt * dk;
-            const float *row = a.u + (size_t)(t0 + tt) * a.ld;
-            sq[i] = apply_act(a.qkv_act, row[a.q_off + head * dk + kk]) * a.q_scale;
-            sk[i] = apply_act(a.qkv_act, row[a.k_off + head * dk + kk]);
-            float dec = head_decay;
-            if (a.w2 != nullptr) {
-                const TW *w = (const TW *)a.w2 + (size_t)(head * dk + kk) * a.rank;
-                float z = a.b2 ? a.b2[head * dk + kk] : 0.f;
-                for (int r = 0; r < a.rank; ++r) z = fmaf(to_f32(w[r]), row[a.r_off + r], z);
-                dec = expf(log_sigmoid_f(z) * a.inv_tau);
+        if (a.w2 != nullptr)
+            for (int i = threadIdx.x; i < n * a.rank; i += SCAN_THREADS) {
+                const int tt = i / a.rank;
+                sr[i] = a.u[(size_t)(t0 + tt) * a.ld + a.r_off + (i - tt * a.rank)];
             }
-            sa[i] = dec;
+        // four elements a thread at a time, their loads ahead of the arithmetic
+        for (int i0 = threadIdx.x; i0 < n * dk; i0 += 4 * SCAN_THREADS) {
+            float qv[4], kv[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int i = i0 + j * SCAN_THREADS;
+                if (i < n * dk) {
+                    const int tt = i / dk, kk = i - tt * dk;
+                    const float *row = a.u + (size_t)(t0 + tt) * a.ld;
+                    qv[j] = row[a.q_off + head * dk + kk];
+                    kv[j] = row[a.k_off + head * dk + kk];
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int i = i0 + j * SCAN_THREADS;
+                if (i < n * dk) {
+                    sq[i] = apply_act(a.qkv_act, qv[j]) * a.q_scale;
+                    sk[i] = apply_act(a.qkv_act, kv[j]);
+                }
+            }
         }
         for (int i = threadIdx.x; i < n * cols; i += SCAN_THREADS) {
             const int tt = i / cols, cc = i - tt * cols;
             sv[i] = c0 + cc < a.dv ? apply_act(a.qkv_act, a.u[(size_t)(t0 + tt) * a.ld + a.v_off + head * a.dv + c0 + cc]) : 0.f;
         }
         __syncthreads();
+        for (int i = threadIdx.x; i < n * dk; i += SCAN_THREADS) {
+            float dec = head_decay;
+            if (a.w2 != nullptr) {
+                const int tt = i / dk, kk = i - tt * dk;
+                const TW *w = (const TW *)a.w2 + (size_t)(head * dk + kk) * a.rank;
+                float z = a.b2 ? a.b2[head * dk + kk] : 0.f;
+                for (int r = 0; r < a.rank; ++r) z = fmaf(to_f32(w[r]), sr[tt * a.rank + r], z);
+                dec = expf(log_sigmoid_f(z) * a.inv_tau);
+            }
+            sa[i] = dec;
+        }
+        __syncthreads();
+        if (write_cum) {            // b_t = a_t * b_(t-1) per channel, from the piece's start
+            for (int kk = threadIdx.x; kk < dk; kk += SCAN_THREADS) {
+                float b = t0 > first ? a.cum[((size_t)(t0 - 1) * a.heads + head) * dk + kk] : 1.f;
+                for (int tt = 0; tt < n; ++tt) {
+                    b *= sa[tt * dk + kk];
+                    a.cum[((size_t)(t0 + tt) * a.heads + head) * dk + kk] = b;
+                }
+            }
+        }
         for (int tt = 0; tt < n; ++tt) {
             const float vv = sv[tt * cols + col];
             const float *q = sq + (size_t)tt * dk + part, *k = sk + (size_t)tt * dk + part, *al = sa + (size_t)tt * dk + part;
@@ -423,32 +487,139 @@ linear_scan_kernel(ScanArgs a) {
     }
 }
 
+// One thread per (request with pieces, head, element of S): the pieces in order.
+__global__ void scan_carry_kernel(ScanArgs a) {
+    pdl_trigger();
+    pdl_wait();
+    const int head = blockIdx.y;
+    const int *pr = a.piece_reqs + 3 * blockIdx.z;
+    const int req = pr[0], p0 = pr[1], np = pr[2];
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= a.dk * a.dv) return;
+    const int kk = e / a.dv;
+    float *slot = a.state + ((size_t)a.slot_ids[req] * a.heads + head) * a.dk * a.dv + e;
+    float run = *slot;
+    for (int p = p0; p < p0 + np; ++p) {
+        float *ps = a.piece_state + ((size_t)p * a.heads + head) * a.dk * a.dv + e;
+        const int first = a.pieces[2 * p], n = a.pieces[2 * p + 1];
+        float d;
+        if (a.w2 != nullptr) {
+            d = a.cum[((size_t)(first + n - 1) * a.heads + head) * a.dk + kk];
+        } else {
+            d = 1.f;
+            const float hd = a.decay[head];
+            for (int i = 0; i < n; ++i) d *= hd;
+        }
+        const float mine = *ps;
+        *ps = run;                  // the state at the piece's start
+        run = fmaf(d, run, mine);
+    }
+    *slot = run;
+}
+
+// out[t, head, v] += sum_k q_t[k] b_t[k] S_start[k, v] for the rows of a piece.  A block owns (piece, head, 64 columns):
+// S_start's slice in shared memory, 16 rows of q * b at a time beside it (transposed, so that a thread reads the eight rows
+// it works on as two vectors); thread (half, column) adds up eight rows against its column.
+constexpr int PFX_COLS = 64, PFX_ROWS = 16, PFX_K = 128;
+
+__global__ void __launch_bounds__(128)
+scan_prefix_kernel(ScanArgs a) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ __align__(16) float Ssm[PFX_K * PFX_COLS];
+    __shared__ __align__(16) float qb[PFX_K * PFX_ROWS];
+    const int p = blockIdx.x, head = blockIdx.y, c0 = blockIdx.z * PFX_COLS;
+    const int first = a.pieces[2 * p], n = a.pieces[2 * p + 1];
+    const int v = threadIdx.x % PFX_COLS, half = threadIdx.x / PFX_COLS;
+    const float *S = a.piece_state + ((size_t)p * a.heads + head) * a.dk * a.dv;
+    const float hd = a.decay ? a.decay[head] : 1.f;
+    for (int k0 = 0; k0 < a.dk; k0 += PFX_K) {
+        const int nk = min(PFX_K, a.dk - k0);
+        __syncthreads();
+        for (int i = threadIdx.x; i < nk * PFX_COLS; i += 128) {
+            const int kk = i / PFX_COLS, cc = i - kk * PFX_COLS;
+            Ssm[i] = c0 + cc < a.dv ? S[(size_t)(k0 + kk) * a.dv + c0 + cc] : 0.f;
+        }
+        for (int t0 = 0; t0 < n; t0 += PFX_ROWS) {
+            const int nt = min(PFX_ROWS, n - t0);
+            __syncthreads();
+            for (int i = threadIdx.x; i < PFX_ROWS * nk; i += 128) {
+                const int tt = i / nk, kk = i - tt * nk;
+                float val = 0.f;
+                if (tt < nt) {
+                    const int t = first + t0 + tt;
+                    float b;
+                    if (a.w2 != nullptr) {
+                        b = a.cum[((size_t)t * a.heads + head) * a.dk + k0 + kk];
+                    } else {
+                        b = hd;
+                        for (int j = 0; j < t0 + tt; ++j) b *= hd;       // the same products, in the same order, as the carry's
+                    }
+                    val = apply_act(a.qkv_act, a.u[(size_t)t * a.ld + a.q_off + head * a.dk + k0 + kk]) * a.q_scale * b;
+                }
+                qb[kk * PFX_ROWS + tt] = val;
+            }
+            __syncthreads();
+            float acc[8];
+#pragma unroll
+            for (int r = 0; r < 8; ++r) acc[r] = 0.f;
+            for (int kk = 0; kk < nk; ++kk) {
+                const float sv = Ssm[kk * PFX_COLS + v];
+                const float4 x = *reinterpret_cast<const float4 *>(qb + kk * PFX_ROWS + half * 8);
+                const float4 y = *reinterpret_cast<const float4 *>(qb + kk * PFX_ROWS + half * 8 + 4);
+                acc[0] = fmaf(x.x, sv, acc[0]); acc[1] = fmaf(x.y, sv, acc[1]); acc[2] = fmaf(x.z, sv, acc[2]); acc[3] = fmaf(x.w, sv, acc[3]);
+                acc[4] = fmaf(y.x, sv, acc[4]); acc[5] = fmaf(y.y, sv, acc[5]); acc[6] = fmaf(y.z, sv, acc[6]); acc[7] = fmaf(y.w, sv, acc[7]);
+            }
+            if (c0 + v < a.dv) {
+#pragma unroll
+                for (int r = 0; r < 8; ++r) {
+                    const int tt = half * 8 + r;
+                    if (tt < nt) a.out[(size_t)(first + t0 + tt) * a.heads * a.dv + head * a.dv + c0 + v] += acc[r];
+                }
+            }
+        }
+    }
+}
+
+// Rows of scratch the pieces of a step of `rows` rows need at most: piece_state floats, cum floats.
+JK_EXPORT long long jk_linear_scan_scratch_floats(int rows, int heads, int dk, int dv, int projected) {
+    return jk::scan_scratch_floats(rows, heads, dk, dv, projected != 0);
+}
+JK_EXPORT int jk_linear_scan_piece() { return SCAN_PIECE; }
+
 JK_EXPORT int jk_linear_scan(const float *u, int ld, int q_off, int k_off, int v_off, int heads, int dk, int dv, int qkv_act,
                              float q_scale, const float *decay, const void *w2, int w2_dtype, const float *b2, int r_off, int rank,
                              float tau, float *state, const int *req_start, const int *slot_ids, int nreq, int T, float *out,
-                             int sms, cudaStream_t stream) {
+                             const int *direct, int n_direct, const int *pieces, int n_pieces, const int *piece_reqs,
+                             int n_piece_reqs, float *scratch, long long scratch_floats, int sms, cudaStream_t stream) {
     if (T == 0 || nreq == 0) return JK_OK;
     JK_REQUIRE(u && state && req_start && slot_ids && out && heads > 0 && dk > 0 && dv > 0, "linear_scan: an argument is missing");
     JK_REQUIRE((decay != nullptr) != (w2 != nullptr), "linear_scan: the decay is a constant per head or projected, one of the two");
     JK_REQUIRE(w2 == nullptr || (rank > 0 && tau > 0.f), "linear_scan: a projected decay of rank %d, tau %g", rank, tau);
     JK_REQUIRE(dk <= 2048, "linear_scan: %d key channels a head exceed 2048", dk);
+    if (n_pieces == 0 && direct == nullptr && n_direct <= 0) n_direct = nreq;        // no lists: every request is one item
+    JK_REQUIRE(n_direct >= 0 && n_pieces >= 0 && n_direct + n_pieces > 0, "linear_scan: nothing to do");
+    JK_REQUIRE(n_pieces == 0 || (pieces && piece_reqs && n_piece_reqs > 0 && scratch), "linear_scan: pieces without their lists or scratch");
+    const long long state_floats = (long long)n_pieces * heads * dk * dv;
+    JK_REQUIRE(n_pieces == 0 || state_floats + (w2 ? (long long)T * heads * dk : 0) <= scratch_floats,
+               "linear_scan: %d pieces need more scratch than %lld floats", n_pieces, scratch_floats);
     // lanes per column: as few as keep a thread's share of a column at 32 channels (64 beyond 1024 channels); more of them,
     // and so fewer columns a block and more blocks, while the blocks do not fill the SMs
     const int sm_count = sms > 0 ? sms : 148;
+    const int items = n_direct + n_pieces;
     int kq = 1;
     while (kq < 32 && (dk + kq - 1) / kq > 32) kq *= 2;
-    while (kq < 32 && (dk + 2 * kq - 1) / (2 * kq) >= 1 && 2 * kq <= dk &&
-           (long long)heads * nreq * ((dv + SCAN_THREADS / kq - 1) / (SCAN_THREADS / kq)) < sm_count)
-        kq *= 2;
+    while (kq < 32 && 2 * kq <= dk && (long long)heads * items * ((dv + SCAN_THREADS / kq - 1) / (SCAN_THREADS / kq)) < sm_count) kq *= 2;
     const int cols = SCAN_THREADS / kq;
     const int per_thread = (dk + kq - 1) / kq;
-    const size_t row_bytes = sizeof(float) * (3 * (size_t)dk + cols);
+    const size_t row_bytes = sizeof(float) * (3 * (size_t)dk + cols + (w2 ? rank : 0));
     int chunk = (int)std::min<size_t>(32, std::max<size_t>(1, (40 * 1024) / row_bytes));
     chunk = std::min(chunk, T);
     ScanArgs a{u, ld, q_off, k_off, v_off, r_off, heads, dk, dv, qkv_act, q_scale, decay, w2, b2, rank, tau > 0.f ? 1.f / tau : 0.f,
-               state, req_start, slot_ids, out, kq, chunk};
-    dim3 grid(heads, nreq, (dv + cols - 1) / cols);
-    JK_REQUIRE(nreq <= 65535 && grid.z <= 65535, "linear_scan: %d requests in one launch", nreq);
+               state, req_start, slot_ids, out, kq, chunk, direct, n_direct, pieces, n_pieces, piece_reqs, scratch,
+               scratch ? scratch + state_floats : nullptr};
+    dim3 grid(heads, items, (dv + cols - 1) / cols);
+    JK_REQUIRE(items <= 65535 && grid.z <= 65535 && heads <= 65535, "linear_scan: %d items in one launch", items);
     const size_t smem = row_bytes * chunk;
 #define SCAN_LAUNCH(TW, KS) jk_launch(linear_scan_kernel<TW, KS>, grid, dim3(SCAN_THREADS), smem, stream, a)
 #define SCAN_LAUNCH_T(TW)                                   \
@@ -466,6 +637,12 @@ JK_EXPORT int jk_linear_scan(const float *u, int ld, int q_off, int k_off, int v
     else
         SCAN_LAUNCH_T(float);
     JK_CHECK_LAUNCH("linear_scan");
+    if (n_pieces > 0) {
+        jk_launch(scan_carry_kernel, dim3((dk * dv + 255) / 256, heads, n_piece_reqs), dim3(256), 0, stream, a);
+        JK_CHECK_LAUNCH("scan_carry");
+        jk_launch(scan_prefix_kernel, dim3(n_pieces, heads, (dv + PFX_COLS - 1) / PFX_COLS), dim3(128), 0, stream, a);
+        JK_CHECK_LAUNCH("scan_prefix");
+    }
     return JK_OK;
 }
 

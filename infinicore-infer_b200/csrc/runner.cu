@@ -447,9 +447,19 @@ int run_linear_attention(Run &r, const RunnerOp &op) {
     if (int rc = r.slot(SLOT_MIX, 4LL * T * op.heads * dv, &mix, "a recurrence's output")) return rc;
     if (int rc = r.slot(op.out_slot, (long long)r.elem() * T * op.heads * dv, &out, "a linear attention's output")) return rc;
     JK_REQUIRE(r.st.slot_ids != nullptr && op.state != nullptr, "runner: a recurrence without its state slots");
+    const int n_pieces = r.st.list_n[op.list_tiles];
+    void *scratch = nullptr;
+    long long scratch_floats = 0;
+    if (n_pieces > 0) {
+        scratch_floats = (long long)n_pieces * op.heads * op.head_dim * dv + (op.rank ? (long long)T * op.heads * op.head_dim : 0);
+        if (int rc = r.slot(SLOT_SCAN, 4 * scratch_floats, &scratch, "the pieces of a recurrence")) return rc;
+    }
     RUN(mixers, g_fns.linear_scan((const float *)u, op.ld, op.q_off, op.k_off, op.v_off, op.heads, op.head_dim, dv, op.act, op.q_scale,
                                   op.decay, op.w2, r.env.dtype, op.b2, op.r_off, op.rank, op.tau, op.state, r.st.req_start, r.st.slot_ids,
-                                  r.st.nreq, T, (float *)mix, r.env.routing.sms, r.stream));
+                                  r.st.nreq, T, (float *)mix, r.st.lists[op.list_short], r.st.list_n[op.list_short],
+                                  r.st.lists[op.list_tiles], n_pieces, r.st.lists[op.list_aux], r.st.list_n[op.list_aux],
+                                  (float *)scratch, scratch_floats, r.env.routing.sms, r.stream));
+    if (n_pieces > 0) g_launches += 2;      // the carry and the prefix kernels
     RUN(mixers, g_fns.norm_gate((const float *)mix, (const float *)u, op.ld, op.g_off, op.vec, op.eps, op.heads, dv, op.per_head_norm,
                                 op.gate_act, out, r.env.dtype, T, r.stream));
     return JK_OK;
@@ -589,6 +599,8 @@ JK_EXPORT int jk_runner_slot_bytes(const RunnerEnv *env, const RunnerOp *ops, in
             case OP_LINEAR_ATTENTION: {
                 const long long width = (long long)op.heads * (op.v_head_dim > 0 ? op.v_head_dim : op.head_dim);
                 need(op.in_slot, 4 * rows * op.ld); need(SLOT_MIX, 4 * rows * width); need(op.out_slot, e * rows * width);
+                if (rows > jk::SCAN_PIECE)
+                    need(SLOT_SCAN, 4 * jk::scan_scratch_floats(rows, op.heads, op.head_dim, op.v_head_dim > 0 ? op.v_head_dim : op.head_dim, op.rank > 0));
                 break;
             }
             default: JK_FAIL(JK_BAD_ARGUMENT, "runner_slot_bytes: record %d has kind %d", i, op.kind);

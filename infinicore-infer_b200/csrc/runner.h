@@ -54,7 +54,8 @@ typedef int (*ConvQkvFn)(const float *, int, int, int, int, int, int, int, int, 
                          const float *, const float *, float, const float *, int, float *, const int *, const int *, const int *,
                          const int *, const int *, int, int, void *, void *, void *, int, int, int, cudaStream_t);
 typedef int (*LinearScanFn)(const float *, int, int, int, int, int, int, int, int, float, const float *, const void *, int, const float *,
-                            int, int, float, float *, const int *, const int *, int, int, float *, int, cudaStream_t);
+                            int, int, float, float *, const int *, const int *, int, int, float *, const int *, int, const int *, int,
+                            const int *, int, float *, long long, int, cudaStream_t);
 typedef int (*NormGateFn)(const float *, const float *, int, int, const float *, float, int, int, int, int, void *, int, int, cudaStream_t);
 typedef int (*ArgmaxFn)(const float *, long long, int, int, int *, void *, cudaStream_t);
 typedef int (*SampleFn)(const float *, long long, int, int, const float *, const int *, const float *, const float *, int *,
@@ -117,6 +118,7 @@ enum RunnerSlot {
     SLOT_TMP,           // float32: the product before an unfused rotation or activation ([T, widest such product])
     SLOT_DECODE,        // float32: partial results of the split-key attention
     SLOT_MIX,           // float32 [T, heads * value size]: a recurrence's output before its norm and gate
+    SLOT_SCAN,          // float32: the states and running decays of a recurrence's pieces
     RUNNER_SLOTS
 };
 
@@ -168,6 +170,8 @@ struct RunnerOp {
     int per_head_norm;          // LINEAR_ATTENTION: 1 norms each head over its values (weight [dv]); 0 all heads at once
     int rank;                   // LINEAR_ATTENTION: width of the decay's projection (0: a constant per head)
     int has_kv;                 // CONV_QKV: 1 makes keys and values too (0: queries only, the cache is another layer's)
+    int list_aux;               // LINEAR_ATTENTION: with list_short (requests run in one go) and list_tiles (pieces), the
+                                // step's list of the requests that have pieces
     float tau, q_scale;         // LINEAR_ATTENTION: decay = sigmoid(z)^(1/tau); factor of q
     const float *conv_q, *conv_k, *conv_v;      // CONV_QKV: [channels, taps]
     const float *norm_q, *norm_k;               // CONV_QKV: weights of the whole-projection RMS norms

@@ -607,17 +607,31 @@ def conv_qkv(u: torch.Tensor, offsets, heads: int, kv_heads: int, dk: int, dv: i
 
 def linear_scan(u: torch.Tensor, offsets, heads: int, dk: int, dv: int, qkv_act: int, q_scale: float, decay: Optional[torch.Tensor],
                 w2: Optional[torch.Tensor], b2: Optional[torch.Tensor], r_off: int, tau: float, state: torch.Tensor,
-                req_start: torch.Tensor, slot_ids: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+                req_start: torch.Tensor, slot_ids: torch.Tensor, out: torch.Tensor, direct: Optional[torch.Tensor] = None,
+                n_direct: int = 0, pieces: Optional[torch.Tensor] = None, piece_reqs: Optional[torch.Tensor] = None) -> torch.Tensor:
     """S = diag(a) S + k v^T, o = S^T q over each request's rows of the fused float32 projections ``u`` (columns
-    ``offsets = (q, k, v)``), from and into ``state [slots, heads, dk, dv]``; ``out`` float32 ``[T, heads * dv]``."""
+    ``offsets = (q, k, v)``), from and into ``state [slots, heads, dk, dv]``; ``out`` float32 ``[T, heads * dv]``.
+    Without lists every request runs in one go; with them (int32: ``direct`` requests, ``pieces [n, 2]`` (first row, rows),
+    ``piece_reqs [m, 3]`` (request, first piece, pieces)) the pieces run side by side and are joined."""
     _need(u, "u", torch.float32); _need(state, "state", torch.float32); _need(out, "out", torch.float32)
     T, nreq = u.shape[0], req_start.numel() - 1
     lib = _build.load("mixers")
+    n_pieces = pieces.numel() // 2 if pieces is not None else 0
+    scratch, floats = None, 0
+    if n_pieces:
+        _need(pieces, "pieces", torch.int32); _need(piece_reqs, "piece_reqs", torch.int32)
+        floats = n_pieces * heads * dk * dv + (T * heads * dk if w2 is not None else 0)
+        scratch = torch.empty(floats, dtype=torch.float32, device=u.device)
+    if direct is not None:
+        _need(direct, "direct", torch.int32)
+        n_direct = direct.numel()
     _check("mixers", lib.jk_linear_scan(
         _ptr(u), _c_int(u.shape[1]), _c_int(offsets[0]), _c_int(offsets[1]), _c_int(offsets[2]), _c_int(heads), _c_int(dk), _c_int(dv),
         _c_int(qkv_act), _c_float(q_scale), _ptr(decay), _ptr(w2), _c_int(dtype_code(w2.dtype) if w2 is not None else F32), _ptr(b2),
         _c_int(r_off), _c_int(w2.shape[1] if w2 is not None else 0), _c_float(tau), _ptr(state), _ptr(req_start), _ptr(slot_ids),
-        _c_int(nreq), _c_int(T), _ptr(out), _c_int(_sm_count(u.device)), _stream()))
+        _c_int(nreq), _c_int(T), _ptr(out), _ptr(direct), _c_int(n_direct), _ptr(pieces), _c_int(n_pieces), _ptr(piece_reqs),
+        _c_int(piece_reqs.numel() // 3 if piece_reqs is not None else 0), _ptr(scratch), _c_ll(floats), _c_int(_sm_count(u.device)),
+        _stream()))
     return out
 
 

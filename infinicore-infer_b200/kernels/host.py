@@ -68,6 +68,11 @@ def attention_tile_rows() -> int:
     return lib().jk_attention_tile_rows()
 
 
+def scan_piece() -> int:
+    """A request with more rows than this in a step has its linear-attention recurrence cut into pieces of this many."""
+    return lib().jk_scan_piece()
+
+
 # ---- the layout of a step's metadata -------------------------------------------------------------------------------
 class StepLayout:
     """Offsets (in int32 elements) of a step's arrays inside the metadata buffer (``jk::StepLayout``)."""

@@ -63,15 +63,51 @@ class LinearAttention:
     def weight_bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in (self.w_in, self.w_o, self.w2) if t is not None)
 
+    # ---- work lists: what this mixer asks every step to carry --------------------------------------------------------
+    # A request that brings at most ``scan_piece()`` rows runs its recurrence in one go from its state slot; the rows of a
+    # longer portion are cut into pieces that run side by side and are then joined (csrc/mixers.cu).  The lists: the requests
+    # of the first kind, (first row, rows) of every piece, and (request, first piece, pieces) of every request that has some.
+    LISTS = ("direct", "pieces", "piece_reqs")
+
+    @staticmethod
+    def step_list_capacity(T: int, B: int) -> Dict[str, int]:
+        from ..kernels import host
+        return {"direct": B, "pieces": 2 * (T // host.scan_piece() + B), "piece_reqs": 3 * B}
+
+    @staticmethod
+    def fill_step_lists(B: int, pad_B: int, lens, starts, arrays) -> Dict[str, tuple]:
+        from ..kernels import host
+        piece = host.scan_piece()
+        direct, pieces, piece_reqs = arrays["direct"], arrays["pieces"], arrays["piece_reqs"]
+        row = n_direct = n_pieces = n_reqs = 0
+        for i in range(B):
+            n = lens[i]
+            if n <= piece:
+                direct[n_direct] = i
+                n_direct += 1
+            else:
+                first = n_pieces
+                for r0 in range(0, n, piece):
+                    pieces[2 * n_pieces], pieces[2 * n_pieces + 1] = row + r0, min(piece, n - r0)
+                    n_pieces += 1
+                piece_reqs[3 * n_reqs: 3 * n_reqs + 3] = (i, first, n_pieces - first)
+                n_reqs += 1
+            row += n
+        for i in range(B, pad_B):
+            direct[n_direct] = i
+            n_direct += 1
+        return {"direct": (n_direct, n_direct == pad_B), "pieces": (n_pieces, False), "piece_reqs": (n_reqs, False)}
+
     def plan_delta(self, program, view, writes_cache: bool = True, state_view=None) -> None:
         """Three records: the fused product (h -> float32 rows), the recurrence with norm and gate (-> o), the output product
         into the delta slot."""
         s = self.spec
         nk, nv = self._widths(s)
         ld = self.w_in.shape[0]
+        direct, pieces, piece_reqs = program.work_lists(LinearAttention, self.LISTS)
         program.emit_records([
             record("linear", "h", "tmp", n=ld, k=s.hidden_size, w=self.w_in),
-            record("linear_attention", "tmp", "o", heads=s.num_heads, head_dim=s.head_dim, v_head_dim=s.v_head_dim, ld=ld,
+            record("linear_attention", "tmp", "o", list_short=direct, list_tiles=pieces, list_aux=piece_reqs, heads=s.num_heads, head_dim=s.head_dim, v_head_dim=s.v_head_dim, ld=ld,
                    q_off=0, k_off=nk, v_off=2 * nk, g_off=2 * nk + nv, r_off=2 * nk + 2 * nv, act=ACT[s.qkv_act], q_scale=s.q_scale,
                    gate_act=ACT[s.gate_act], per_head_norm=s.norm_per_head, eps=s.norm_eps, vec=self.norm, decay=self.decay,
                    w2=self.w2, b2=self.b2, rank=s.decay_rank if s.decay is None else 0, tau=s.decay_tau, state=view.state),

@@ -24,7 +24,7 @@ from ..kernels import host as _host
 
 _i, _f, _p, _ll = ctypes.c_int, ctypes.c_float, ctypes.c_void_p, ctypes.c_longlong
 
-SLOTS = ("x", "delta", "h", "q", "o", "act", "hw", "logits", "tmp", "decode", "mix")       # RunnerSlot of csrc/runner.h
+SLOTS = ("x", "delta", "h", "q", "o", "act", "hw", "logits", "tmp", "decode", "mix", "scan")       # RunnerSlot of csrc/runner.h
 SLOT = {name: i for i, name in enumerate(SLOTS)}
 OP_NAMES = {1: "embed", 2: "norm", 3: "qkv", 4: "attention", 5: "residual", 6: "gate_up", 7: "linear", 8: "cast",
             9: "layernorm", 10: "conv_qkv", 11: "linear_attention"}
@@ -44,7 +44,7 @@ class RunnerOp(ctypes.Structure):
                 + [("num_pages", _i)]
                 # what the mixers of csrc/mixers.cu add (all zero in the records of the plain decoder)
                 + [(n, _i) for n in ("v_head_dim", "sink", "gated", "act", "gate_act", "ld", "q_off", "k_off", "v_off", "g_off", "r_off",
-                                     "taps", "rot_dims", "per_head_norm", "rank", "has_kv")]
+                                     "taps", "rot_dims", "per_head_norm", "rank", "has_kv", "list_aux")]
                 + [(n, _f) for n in ("tau", "q_scale")]
                 + [(n, _p) for n in ("conv_q", "conv_k", "conv_v", "norm_q", "norm_k", "freq", "decay", "w2", "b2", "bias", "state")])
 
@@ -173,7 +173,7 @@ class HostIO:
         """``[rows, width]`` of a slot (the activations' type unless said otherwise; ``x`` and ``delta`` are float32)."""
         rows = self.rows if rows is None else rows
         if dtype is None:
-            dtype = torch.float32 if slot in ("x", "delta", "logits", "tmp", "decode", "mix") else self._runner.runtime.dtype
+            dtype = torch.float32 if slot in ("x", "delta", "logits", "tmp", "decode", "mix", "scan") else self._runner.runtime.dtype
         raw = self._runner.slot_tensor(slot)
         need = rows * width * torch.empty((), dtype=dtype).element_size()
         if need > raw.numel():

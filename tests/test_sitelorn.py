@@ -258,8 +258,9 @@ def test_recurrence_carries_its_state_across_cuts_and_slots(H, dk, dv, projected
     decaying it wrongly, moves late outputs."""
     from infinicore_infer_b200 import kernels as K
     dev = torch.device("cuda:0")
+    from infinicore_infer_b200.parts import LinearAttention
     rank, tau = 5, 6.0
-    T = 90
+    T = 230
     u, ld = scan_inputs(T, H, dk, dv, rank, 5)
     u2, _ = scan_inputs(T, H, dk, dv, rank, 6)
     u[1, H * dk: 2 * H * dk] *= 6.0           # an early key that late rows still see
@@ -285,14 +286,20 @@ def test_recurrence_carries_its_state_across_cuts_and_slots(H, dk, dv, projected
     state[0] = 7.0                              # slot 0 is nobody's; what lies there must not matter
     slots = torch.tensor([3, 1], dtype=torch.int32, device=dev)
     got = [[], []]
-    cuts = [0, 1, 2, 30, 31, 64, T]
+    cuts = [0, 1, 2, 30, 31, 160, 225, T]       # 129 rows in one portion: two whole pieces and one row more
     for a, b in zip(cuts, cuts[1:]):
         n = b - a
         rows = torch.cat([u[a:b], u2[a:b]]).float().to(dev)
         out = torch.empty(2 * n, H * dv, dtype=torch.float32, device=dev)
+        caps = LinearAttention.step_list_capacity(2 * n, 2)
+        arrays = {name: np.zeros(max(1, c), dtype=np.int32) for name, c in caps.items()}
+        counts = LinearAttention.fill_step_lists(2, 2, [n, n], [a, a], arrays)
+        lists = {name: torch.from_numpy(arrays[name][:max(1, counts[name][0] * w)]).to(dev) if counts[name][0] else None
+                 for name, w in (("direct", 1), ("pieces", 2), ("piece_reqs", 3))}
         K.linear_scan(rows, offs, H, dk, dv, K.ACT_NONE, 0.5, None if projected else decay.float().to(dev),
                       w2.float().to(dev) if projected else None, b2.float().to(dev) if projected else None, r_off, tau, state,
-                      torch.tensor([0, n, 2 * n], dtype=torch.int32, device=dev), slots, out)
+                      torch.tensor([0, n, 2 * n], dtype=torch.int32, device=dev), slots, out, direct=lists["direct"],
+                      pieces=lists["pieces"], piece_reqs=lists["piece_reqs"])
         got[0].append(out[:n].cpu()); got[1].append(out[n:].cpu())
     for i in range(2):
         o = torch.cat(got[i]).double()
