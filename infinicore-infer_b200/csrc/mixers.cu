@@ -374,6 +374,7 @@ struct ScanArgs {
 };
 
 constexpr int SCAN_THREADS = 128;
+constexpr int SCAN_CPT = 2;         // columns of S a thread keeps: what it reads of a row's q, k and decay serves both
 
 template <typename TW, int KS>      // KS: key channels per thread
 __global__ void __launch_bounds__(SCAN_THREADS)
@@ -381,15 +382,15 @@ linear_scan_kernel(ScanArgs a) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ __align__(16) float sm[];
-    const int kq = a.kq, cols = SCAN_THREADS / kq, dk = a.dk;
+    const int kq = a.kq, cols = SCAN_THREADS / kq * SCAN_CPT, dk = a.dk;
     const int head = blockIdx.x, item = blockIdx.y, c0 = blockIdx.z * cols;
-    float *sq = sm;                                     // [chunk, dk]
-    float *sk = sq + (size_t)a.chunk * dk;              // [chunk, dk]
-    float *sa = sk + (size_t)a.chunk * dk;              // [chunk, dk]
-    float *sv = sa + (size_t)a.chunk * dk;              // [chunk, cols]
+    float4 *sx = reinterpret_cast<float4 *>(sm);        // [chunk, dk] (decay, k, q, -) of a row's channel, side by side
+    float *sv = sm + 4 * (size_t)a.chunk * dk;          // [chunk, cols]
     float *sr = sv + (size_t)a.chunk * cols;            // [chunk, rank]
-    const int col = threadIdx.x / kq, part = threadIdx.x % kq;
-    const bool live = c0 + col < a.dv;
+    const int col = threadIdx.x / kq * SCAN_CPT, part = threadIdx.x % kq;
+    bool live[SCAN_CPT];
+#pragma unroll
+    for (int c = 0; c < SCAN_CPT; ++c) live[c] = c0 + col + c < a.dv;
     int first, last;
     float *S;
     const bool piece = item >= a.n_direct;
@@ -402,9 +403,11 @@ linear_scan_kernel(ScanArgs a) {
         first = a.pieces[2 * p]; last = first + a.pieces[2 * p + 1];
         S = a.piece_state + (((size_t)p * a.heads + head) * dk) * a.dv + c0 + col;
     }
-    float s[KS];
+    float s[SCAN_CPT][KS];
 #pragma unroll
-    for (int i = 0; i < KS; ++i) s[i] = (!piece && live && part + i * kq < dk) ? S[(size_t)(part + i * kq) * a.dv] : 0.f;
+    for (int c = 0; c < SCAN_CPT; ++c)
+#pragma unroll
+        for (int i = 0; i < KS; ++i) s[c][i] = (!piece && live[c] && part + i * kq < dk) ? S[(size_t)(part + i * kq) * a.dv + c] : 0.f;
     const float head_decay = a.decay ? a.decay[head] : 1.f;
     const bool write_cum = piece && a.w2 != nullptr && blockIdx.z == 0;
     for (int t0 = first; t0 < last; t0 += a.chunk) {
@@ -432,8 +435,9 @@ linear_scan_kernel(ScanArgs a) {
             for (int j = 0; j < 4; ++j) {
                 const int i = i0 + j * SCAN_THREADS;
                 if (i < n * dk) {
-                    sq[i] = apply_act(a.qkv_act, qv[j]) * a.q_scale;
-                    sk[i] = apply_act(a.qkv_act, kv[j]);
+                    sx[i].y = apply_act(a.qkv_act, kv[j]);
+                    sx[i].z = apply_act(a.qkv_act, qv[j]) * a.q_scale;
+                    if (a.w2 == nullptr) sx[i].x = head_decay;
                 }
             }
         }
@@ -442,52 +446,60 @@ linear_scan_kernel(ScanArgs a) {
             sv[i] = c0 + cc < a.dv ? apply_act(a.qkv_act, a.u[(size_t)(t0 + tt) * a.ld + a.v_off + head * a.dv + c0 + cc]) : 0.f;
         }
         __syncthreads();
-        for (int i = threadIdx.x; i < n * dk; i += SCAN_THREADS) {
-            float dec = head_decay;
-            if (a.w2 != nullptr) {
+        if (a.w2 != nullptr) {
+            for (int i = threadIdx.x; i < n * dk; i += SCAN_THREADS) {
                 const int tt = i / dk, kk = i - tt * dk;
                 const TW *w = (const TW *)a.w2 + (size_t)(head * dk + kk) * a.rank;
                 float z = a.b2 ? a.b2[head * dk + kk] : 0.f;
                 for (int r = 0; r < a.rank; ++r) z = fmaf(to_f32(w[r]), sr[tt * a.rank + r], z);
-                dec = expf(log_sigmoid_f(z) * a.inv_tau);
+                sx[i].x = expf(log_sigmoid_f(z) * a.inv_tau);
             }
-            sa[i] = dec;
+            __syncthreads();
         }
-        __syncthreads();
         if (write_cum) {            // b_t = a_t * b_(t-1) per channel, from the piece's start
             for (int kk = threadIdx.x; kk < dk; kk += SCAN_THREADS) {
                 float b = t0 > first ? a.cum[((size_t)(t0 - 1) * a.heads + head) * dk + kk] : 1.f;
                 for (int tt = 0; tt < n; ++tt) {
-                    b *= sa[tt * dk + kk];
+                    b *= sx[tt * dk + kk].x;
                     a.cum[((size_t)(t0 + tt) * a.heads + head) * dk + kk] = b;
                 }
             }
         }
         for (int tt = 0; tt < n; ++tt) {
-            const float vv = sv[tt * cols + col];
-            const float *q = sq + (size_t)tt * dk + part, *k = sk + (size_t)tt * dk + part, *al = sa + (size_t)tt * dk + part;
-            float o0 = 0.f, o1 = 0.f;
+            float vv[SCAN_CPT], o[SCAN_CPT];
+#pragma unroll
+            for (int c = 0; c < SCAN_CPT; ++c) { vv[c] = sv[tt * cols + col + c]; o[c] = 0.f; }
+            const float4 *x = sx + (size_t)tt * dk + part;
 #pragma unroll
             for (int i = 0; i < KS; ++i) {
                 if (part + i * kq < dk) {
-                    s[i] = fmaf(al[i * kq], s[i], k[i * kq] * vv);
-                    if (i & 1) o1 = fmaf(s[i], q[i * kq], o1);
-                    else o0 = fmaf(s[i], q[i * kq], o0);
+                    const float4 e = x[i * kq];
+#pragma unroll
+                    for (int c = 0; c < SCAN_CPT; ++c) {
+                        s[c][i] = fmaf(e.x, s[c][i], e.y * vv[c]);
+                        o[c] = fmaf(s[c][i], e.z, o[c]);
+                    }
                 }
             }
-            float o = o0 + o1;
-            for (int off = kq >> 1; off > 0; off >>= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
-            if (part == 0 && live) a.out[(size_t)(t0 + tt) * a.heads * a.dv + head * a.dv + c0 + col] = o;
+#pragma unroll
+            for (int c = 0; c < SCAN_CPT; ++c) {
+                float sum = o[c];
+                for (int off = kq >> 1; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+                if (part == 0 && live[c]) a.out[(size_t)(t0 + tt) * a.heads * a.dv + head * a.dv + c0 + col + c] = sum;
+            }
         }
     }
-    if (live) {
 #pragma unroll
-        for (int i = 0; i < KS; ++i)
-            if (part + i * kq < dk) S[(size_t)(part + i * kq) * a.dv] = s[i];
-    }
+    for (int c = 0; c < SCAN_CPT; ++c)
+        if (live[c]) {
+#pragma unroll
+            for (int i = 0; i < KS; ++i)
+                if (part + i * kq < dk) S[(size_t)(part + i * kq) * a.dv + c] = s[c][i];
+        }
 }
 
-// One thread per (request with pieces, head, element of S): the pieces in order.
+// One thread per (request with pieces, head, element of S): the pieces in order.  What a piece brings (its end state and
+// its decay) does not depend on the running state, so the loads of eight pieces go out before the chain uses them.
 __global__ void scan_carry_kernel(ScanArgs a) {
     pdl_trigger();
     pdl_wait();
@@ -497,22 +509,44 @@ __global__ void scan_carry_kernel(ScanArgs a) {
     const int e = blockIdx.x * blockDim.x + threadIdx.x;
     if (e >= a.dk * a.dv) return;
     const int kk = e / a.dv;
+    const size_t stride = (size_t)a.heads * a.dk * a.dv;
     float *slot = a.state + ((size_t)a.slot_ids[req] * a.heads + head) * a.dk * a.dv + e;
+    float *ps = a.piece_state + ((size_t)p0 * a.heads + head) * a.dk * a.dv + e;
     float run = *slot;
-    for (int p = p0; p < p0 + np; ++p) {
-        float *ps = a.piece_state + ((size_t)p * a.heads + head) * a.dk * a.dv + e;
-        const int first = a.pieces[2 * p], n = a.pieces[2 * p + 1];
-        float d;
-        if (a.w2 != nullptr) {
-            d = a.cum[((size_t)(first + n - 1) * a.heads + head) * a.dk + kk];
-        } else {
-            d = 1.f;
-            const float hd = a.decay[head];
-            for (int i = 0; i < n; ++i) d *= hd;
+    // a constant decay to the power of a whole piece's rows (every piece but the last has that many)
+    float d_whole = 1.f;
+    if (a.w2 == nullptr) {
+        const float hd = a.decay[head];
+        for (int i = 0; i < SCAN_PIECE; ++i) d_whole *= hd;
+    }
+    for (int b0 = 0; b0 < np; b0 += 8) {
+        float mine[8], d[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int p = b0 + j;
+            if (p < np) {
+                mine[j] = ps[(size_t)p * stride];
+                const int first = a.pieces[2 * (p0 + p)], n = a.pieces[2 * (p0 + p) + 1];
+                if (a.w2 != nullptr) {
+                    d[j] = a.cum[((size_t)(first + n - 1) * a.heads + head) * a.dk + kk];
+                } else if (n == SCAN_PIECE) {
+                    d[j] = d_whole;
+                } else {
+                    const float hd = a.decay[head];
+                    float x = 1.f;
+                    for (int i = 0; i < n; ++i) x *= hd;
+                    d[j] = x;
+                }
+            }
         }
-        const float mine = *ps;
-        *ps = run;                  // the state at the piece's start
-        run = fmaf(d, run, mine);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int p = b0 + j;
+            if (p < np) {
+                ps[(size_t)p * stride] = run;          // the state at the piece's start
+                run = fmaf(d[j], run, mine[j]);
+            }
+        }
     }
     *slot = run;
 }
@@ -609,10 +643,12 @@ JK_EXPORT int jk_linear_scan(const float *u, int ld, int q_off, int k_off, int v
     const int items = n_direct + n_pieces;
     int kq = 1;
     while (kq < 32 && (dk + kq - 1) / kq > 32) kq *= 2;
-    while (kq < 32 && 2 * kq <= dk && (long long)heads * items * ((dv + SCAN_THREADS / kq - 1) / (SCAN_THREADS / kq)) < sm_count) kq *= 2;
-    const int cols = SCAN_THREADS / kq;
+    while (kq < 32 && 2 * kq <= dk &&
+           (long long)heads * items * ((dv + SCAN_THREADS / kq * SCAN_CPT - 1) / (SCAN_THREADS / kq * SCAN_CPT)) < sm_count)
+        kq *= 2;
+    const int cols = SCAN_THREADS / kq * SCAN_CPT;
     const int per_thread = (dk + kq - 1) / kq;
-    const size_t row_bytes = sizeof(float) * (3 * (size_t)dk + cols + (w2 ? rank : 0));
+    const size_t row_bytes = sizeof(float) * (4 * (size_t)dk + cols + (w2 ? rank : 0));
     int chunk = (int)std::min<size_t>(32, std::max<size_t>(1, (40 * 1024) / row_bytes));
     chunk = std::min(chunk, T);
     ScanArgs a{u, ld, q_off, k_off, v_off, r_off, heads, dk, dv, qkv_act, q_scale, decay, w2, b2, rank, tau > 0.f ? 1.f / tau : 0.f,
