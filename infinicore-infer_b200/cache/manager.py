@@ -147,6 +147,14 @@ class CacheManager:
         """Go back to ``new_len`` cached positions (new_len <= the current length)."""
         if new_len > self.lengths[req]:
             raise ValueError(f"request {req!r} holds {self.lengths[req]} positions, cannot truncate to {new_len}")
+        if new_len < self.lengths[req] and self._state_tensors:
+            # state that is carried from token to token keeps no history: a request can go back to its start only
+            if new_len != 0:
+                raise ValueError(f"request {req!r}: a model with per-request state cannot go back to position {new_len} "
+                                 f"of {self.lengths[req]}; start it again from 0")
+            slot = self.slots.slot_of(req)
+            for st in self._state_tensors:
+                st[slot].zero_()
         for g in self.groups:
             g.truncate(req, new_len)
         self.lengths[req] = new_len

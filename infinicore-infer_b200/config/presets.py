@@ -41,4 +41,14 @@ PRESETS: Dict[str, Preset] = {
                       num_key_value_heads=2, intermediate_size=16384, vocab_size=73448, max_position_embeddings=4096,
                       rms_norm_eps=1e-5, rope_theta=10000.0, scale_emb=12, scale_depth=1.4, dim_model_base=256,
                       tie_word_embeddings=False, eos_token_id=2), 0.02, 0.01, 16),
+    # a small Sitelorn: every kind of layer, a layer that borrows its keys, one without feed-forward
+    "sitelorn-tiny": Preset(dict(
+        architecture="Sitelorn", vocab=320, width=96, embedding={"scale": 4.0}, norm={"eps": 1e-5}, layers=[
+            {"type": "lightning", "mixer": {"heads": 3, "dim": 16, "vdim": 32, "decay": [0.7, 0.97, 0.999]}, "mlp": {"kind": "dense", "ff": 160}},
+            {"type": "attention", "mixer": {"heads": 4, "kv_heads": 2, "dim": 24, "vdim": 24, "conv": 3, "rot": {"dims": 12, "base": 1e5},
+                                            "scale": 0.2, "mask": {"size": 48}}, "mlp": {"kind": "dense", "ff": 160}},
+            {"type": "gla", "mixer": {"heads": 2, "dim": 24, "vdim": 48, "tau": 8.0, "rank": 8}, "mlp": None},
+            {"type": "attention", "mixer": {"heads": 4, "kv_heads": 2, "dim": 24, "vdim": 24, "conv": 3, "rot": {"dims": 12, "base": 1e5},
+                                            "scale": 0.2, "mask": {"size": 24}, "kv_from": 1}, "mlp": {"kind": "dense", "ff": 160}},
+        ]), 0.1, 0.05, 16),
 }

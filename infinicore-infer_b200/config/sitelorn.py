@@ -113,6 +113,19 @@ class SitelornConfig:
                    layers=tuple(checked),
                    max_positions=int(max_tokens) if max_tokens else int(cfg.get("max_positions", DEFAULT_MAX_POSITIONS)))
 
+    # what the entry points ask of any configuration
+    @property
+    def max_position_embeddings(self) -> int:
+        return self.max_positions
+
+    @property
+    def tie_word_embeddings(self) -> bool:
+        return False
+
+    @property
+    def vocab_size(self) -> int:
+        return self.vocab
+
     def to_dict(self) -> dict:
         """config.json contents that read back to this configuration."""
         return {"architecture": "Sitelorn", "embedding": {"scale": self.embedding_scale}, "norm": {"eps": self.norm_eps},

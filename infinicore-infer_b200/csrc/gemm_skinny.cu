@@ -27,6 +27,7 @@ struct SkArgs {
     int mpad;           // activation rows padded to a multiple of 32 (the MMA's N)
     int stages;         // depth of the ring
     int ksteps;         // 64-wide steps of K per block
+    int gate_act;       // SK_SWIGLU: JkGateAct of the gate
 };
 
 template <int EPI>
@@ -134,7 +135,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                     for (int i = 0; i < 32; ++i) {
                         const int m = c0 + i;
                         const float g = __uint_as_float(v[i]), u = xch[m * 64 + quarter * 32 + lane];
-                        if (m < a.M && n < a.N) out[(size_t)m * a.ldo + n] = __float2bfloat16_rn(g / (1.f + expf(-g)) * u);
+                        if (m < a.M && n < a.N) out[(size_t)m * a.ldo + n] = __float2bfloat16_rn(gated_unit(a.gate_act, g, u));
                     }
                 }
             }
@@ -172,13 +173,15 @@ JK_EXPORT int jk_gemm_skinny_supports(int M, int N, int K) { return M >= 1 && M 
 // [2N, K]; out = silu(gate) * up, bfloat16).
 JK_EXPORT int jk_gemm_skinny(const void *act, const void *w, void *out, int M, int N, int K, int ldo, int epilogue, float scale,
                              int *status, int sms, cudaStream_t stream) {
+    const int gate_act = jk_epilogue_gate(epilogue);
+    epilogue = jk_epilogue_code(epilogue);
     JK_REQUIRE(jk_gemm_skinny_supports(M, N, K), "gemm_skinny: M %d N %d K %d (1 to 128 rows, K a multiple of 8)", M, N, K);
     JK_REQUIRE(epilogue == EPI_F32 || epilogue == EPI_RESIDUAL || epilogue == EPI_SWIGLU, "gemm_skinny: epilogue %d", epilogue);
     JK_REQUIRE(ldo >= N && status != nullptr && out != nullptr, "gemm_skinny: output stride %d < N %d, or a pointer is missing", ldo, N);
     JK_REQUIRE((reinterpret_cast<uintptr_t>(act) & 15) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0,
                "gemm_skinny: operands must be 16-byte aligned");
     if (sms <= 0) sms = 148;
-    SkArgs a{out, M, N, K, ldo, scale, status, (M + 31) / 32 * 32, 0, 0};
+    SkArgs a{out, M, N, K, ldo, scale, status, (M + 31) / 32 * 32, 0, 0, gate_act};
     const int out_rows = epilogue == EPI_SWIGLU ? 64 : 128;
     const int tiles = (N + out_rows - 1) / out_rows;
     const int nk = (K + TG_BK - 1) / TG_BK;

@@ -58,6 +58,7 @@ struct TgArgs {
     int ksplit;        // EPI_RESIDUAL by TMA only: a tile's K is cut into this many units whose partial products all add
                        // themselves into the output (0 or 1: none)
     QkvDest qkv;       // EPI_QKV only
+    int gate_act;      // EPI_SWIGLU: JkGateAct of the gate
 };
 
 template <int BN, int CTAS> struct TgSmem {
@@ -330,7 +331,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
                         for (int i = 0; i < 32; ++i) {
                             const float g = __uint_as_float(v[i]);
-                            f[i] = g / (1.f + expf(-g)) * __uint_as_float(u[i]);
+                            f[i] = gated_unit(a.gate_act, g, __uint_as_float(u[i]));
                         }
                     } else {
 #pragma unroll
@@ -504,6 +505,8 @@ JK_EXPORT int jk_gemm_tcgen05_supports(int M, int N, int K) { return M >= 1 && N
 
 JK_EXPORT int jk_gemm_tcgen05(const void *act, const void *w, void *out, int M, int N, int K, int ldo, int epilogue,
                               float scale, int *status, int sms, cudaStream_t stream) {
+    const int gate_act = jk_epilogue_gate(epilogue);
+    epilogue = jk_epilogue_code(epilogue);
     JK_REQUIRE(jk_gemm_tcgen05_supports(M, N, K), "gemm_tcgen05: M %d N %d K %d (K must be a multiple of 8)", M, N, K);
     JK_REQUIRE(epilogue >= EPI_F32 && epilogue <= EPI_SWIGLU, "gemm_tcgen05: epilogue %d", epilogue);
     JK_REQUIRE(ldo >= N && status != nullptr, "gemm_tcgen05: output stride %d < N %d, or no status word", ldo, N);
@@ -514,7 +517,7 @@ JK_EXPORT int jk_gemm_tcgen05(const void *act, const void *w, void *out, int M, 
     const int out_bytes = (epilogue == EPI_F32 || epilogue == EPI_RESIDUAL) ? 4 : 2;
     CUtensorMap ma, mw, mo;
     if (int rc = tensor_map_2d(act, M, K, K, TG_BM, TG_BK, 2, &ma)) return rc;
-    TgArgs a{out, M, N, K, ldo, scale, status, 0, 0, QkvDest{}};
+    TgArgs a{out, M, N, K, ldo, scale, status, 0, 0, QkvDest{}, gate_act};
     // the output goes out by TMA when its rows are 16-byte aligned, else straight from registers
     a.direct = ((size_t)ldo * out_bytes) % 16 != 0 || (reinterpret_cast<uintptr_t>(out) & 15) != 0;
     if (a.direct) mo = ma;

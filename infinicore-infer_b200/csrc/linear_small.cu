@@ -66,6 +66,7 @@ struct SmallLinearArgs {
     SmallQkvDest qkv;           // EPI_QKV only
     SmallNormFuse norm;         // the tile kernel only
     int *fault;                 // the TMA tile kernel: receives 1 when its bounded wait runs out, 2 for misaligned shared memory
+    int gate_act;               // EPI_SWIGLU: JkGateAct of the gate
 };
 
 constexpr int SL_MAX_WARPS = 8;
@@ -215,7 +216,7 @@ small_linear_kernel(SmallLinearArgs a) {
                         } else {
                             const float gate = acc[0][m][c], up = acc[NW - 1][m][c];
                             reinterpret_cast<__nv_bfloat16 *>(a.out)[(size_t)row * a.ldo + n] =
-                                __float2bfloat16_rn(gate / (1.f + expf(-gate)) * up);
+                                __float2bfloat16_rn(gated_unit(a.gate_act, gate, up));
                         }
                     }
                 }
@@ -533,7 +534,7 @@ small_linear_tile_kernel(const __grid_constant__ CUtensorMap map_w, SmallLinearA
                     const float gate = acc[m][c], up = acc[m][c + 2];
                     if (n < a.N && row < a.M)
                         reinterpret_cast<__nv_bfloat16 *>(a.out)[(size_t)row * a.ldo + n] =
-                            __float2bfloat16_rn(gate / (1.f + expf(-gate)) * up);
+                            __float2bfloat16_rn(gated_unit(a.gate_act, gate, up));
                 }
             }
     }
@@ -732,6 +733,8 @@ JK_EXPORT int jk_linear_small_norm_supports(int M, int N, int K) {
 
 static int linear_small_impl(const void *act, const void *w, void *out, int M, int N, int K, int ldo,
                              int epilogue, int sms, const SmallNormFuse &norm, bool fused, cudaStream_t stream) {
+    const int gate_act = jk_epilogue_gate(epilogue);
+    epilogue = jk_epilogue_code(epilogue);
     JK_REQUIRE(jk_linear_small_supports(M, N, K), "linear_small: M %d N %d K %d is outside what the kernel takes "
                "(1..16 rows, K a multiple of 32)", M, N, K);
     JK_REQUIRE(epilogue == EPI_F32 || epilogue == EPI_SWIGLU || (fused && epilogue == EPI_RESIDUAL), "linear_small: epilogue %d", epilogue);
@@ -748,6 +751,7 @@ static int linear_small_impl(const void *act, const void *w, void *out, int M, i
         const size_t smem = small_tile_smem(K, MT, ksplit);
         if (smem <= 200 * 1024) {
             SmallLinearArgs a{(const __nv_bfloat16 *)act, (const __nv_bfloat16 *)w, out, M, N, K, ldo, ksplit, 0, SmallQkvDest{}, norm};
+            a.gate_act = gate_act;
             if (MT == 1 && epilogue == EPI_F32) return launch_tile<1, EPI_F32>(a, smem, stream);
             if (MT == 2 && epilogue == EPI_F32) return launch_tile<2, EPI_F32>(a, smem, stream);
             if (MT == 1 && epilogue == EPI_RESIDUAL) return launch_tile<1, EPI_RESIDUAL>(a, smem, stream);
@@ -769,6 +773,7 @@ static int linear_small_impl(const void *act, const void *w, void *out, int M, i
     const int tiles_per_unit = warps / ksplit;
     SmallLinearArgs a{(const __nv_bfloat16 *)act, (const __nv_bfloat16 *)w, out, M, N, K, ldo, ksplit,
                       (tiles + tiles_per_unit - 1) / tiles_per_unit, SmallQkvDest{}};
+            a.gate_act = gate_act;
     const int ring = small_linear_ring(K, MT, warps);
     const size_t smem = small_linear_smem(K, MT, warps, ring);
     int per_sm = (int)((220 * 1024) / (smem + 1024));

@@ -335,30 +335,26 @@ int run_gate_up(Run &r, const RunnerOp &op, const FusedNorm &fused) {
     void *h, *act;
     if (int rc = r.slot(op.in_slot, (long long)r.elem() * T * d, &h, "gate/up's activations")) return rc;
     if (int rc = r.slot(op.out_slot, (long long)r.elem() * T * di, &act, "the feed-forward's inner activations")) return rc;
-    if (op.act != RUNNER_ACT_NONE && op.act != RUNNER_ACT_SILU) {
-        // a gate of another kind than silu: the product in float32, then the gated unit's own kernel
-        JK_REQUIRE(g_fns.glu != nullptr, "runner: a gated unit with activation %d needs the mixers module", op.act);
-        void *gu;
-        if (int rc = r.slot(SLOT_TMP, 4LL * T * 2 * di, &gu, "the gate/up product")) return rc;
-        if (int rc = product_f32(r, h, op.w, nullptr, (float *)gu, T, 2 * di, d)) return rc;
-        RUN(mixers, g_fns.glu((const float *)gu, act, r.env.dtype, T, di, op.act, r.stream));
-        return JK_OK;
-    }
+    // the gate's activation rides above the epilogue's code (common.cuh: gated_unit)
+    JK_REQUIRE(op.act == RUNNER_ACT_NONE || op.act == RUNNER_ACT_SILU || op.act == RUNNER_ACT_GELU_TANH,
+               "runner: a gated unit with activation %d is not built", op.act);
+    const bool gelu = op.act == RUNNER_ACT_GELU_TANH;
+    const int gate_bits = gelu ? (RUNNER_ACT_GELU_TANH << 8) : 0;
     if (fused.norm != nullptr) {
-        RUN(linear_small, g_fns.linear_small_norm(h, op.w, act, T, di, d, di, 1, fused.sumsq, fused.norm->eps, nullptr, nullptr, nullptr,
+        RUN(linear_small, g_fns.linear_small_norm(h, op.w, act, T, di, d, di, 1 | gate_bits, fused.sumsq, fused.norm->eps, nullptr, nullptr, nullptr,
                                                   1.f, r.env.status, ro.sms, r.stream));
         return JK_OK;
     }
     if (r.env.dtype == JK_BF16) {
         switch (r.route(T, di, d, jk::PRODUCT_SWIGLU)) {
             case jk::ROUTE_SMALL:
-                RUN(linear_small, g_fns.linear_small(h, op.w, act, T, di, d, di, 1, ro.sms, r.stream));
+                RUN(linear_small, g_fns.linear_small(h, op.w, act, T, di, d, di, 1 | gate_bits, ro.sms, r.stream));
                 return JK_OK;
             case jk::ROUTE_SKINNY:
-                RUN(gemm_tcgen05, g_fns.gemm_skinny(h, op.w, act, T, di, d, di, 3, 1.f, r.env.status, ro.sms, r.stream));
+                RUN(gemm_tcgen05, g_fns.gemm_skinny(h, op.w, act, T, di, d, di, 3 | gate_bits, 1.f, r.env.status, ro.sms, r.stream));
                 return JK_OK;
             case jk::ROUTE_TCGEN05:
-                RUN(gemm_tcgen05, g_fns.gemm_tcgen05(h, op.w, act, T, di, d, di, 3, 1.f, r.env.status, ro.sms, r.stream));
+                RUN(gemm_tcgen05, g_fns.gemm_tcgen05(h, op.w, act, T, di, d, di, 3 | gate_bits, 1.f, r.env.status, ro.sms, r.stream));
                 return JK_OK;
             default:
                 break;
@@ -370,6 +366,11 @@ int run_gate_up(Run &r, const RunnerOp &op, const FusedNorm &fused) {
         RUN(elementwise, g_fns.gemm_f32((const float *)h, d, (const float *)op.w, d, nullptr, (float *)tmp, 2 * di, T, 2 * di, d, r.stream));
     } else {
         if (int rc = lt_product(h, op.w, (float *)tmp, T, 2 * di, d, r.buf, r.stream)) return rc;
+    }
+    if (gelu) {
+        JK_REQUIRE(g_fns.glu != nullptr, "runner: the unfused gated unit with activation %d needs the mixers module", op.act);
+        RUN(mixers, g_fns.glu((const float *)tmp, act, r.env.dtype, T, di, op.act, r.stream));
+        return JK_OK;
     }
     RUN(elementwise, g_fns.swiglu(tmp, JK_F32, act, r.env.dtype, T, di, r.stream));
     return JK_OK;
