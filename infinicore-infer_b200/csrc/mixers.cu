@@ -43,7 +43,16 @@ __device__ __forceinline__ float apply_act(int act, float z) {
 //   add mode   (x_add != null): v = delta[r]; x[r] += y; h[r] = T(x[r]) if h is given      (norm on a sublayer's output)
 //   rows mode  (x_add == null): v = x[rows ? rows[i] : i]; out[i] = T(y)                     (a norm that feeds a product)
 // ---------------------------------------------------------------------------------------------------------------
-template <typename T>
+__device__ __forceinline__ void store4_as(float *p, float4 v) { *reinterpret_cast<float4 *>(p) = v; }
+__device__ __forceinline__ void store4_as(__nv_bfloat16 *p, float4 v) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 raw;
+    raw.x = *reinterpret_cast<const unsigned *>(&lo); raw.y = *reinterpret_cast<const unsigned *>(&hi);
+    *reinterpret_cast<uint2 *>(p) = raw;
+}
+
+// VEC: the width is a multiple of 4 (rows of every operand then start on 16-byte boundaries: four elements move at a time)
+template <typename T, bool VEC>
 __global__ void layernorm_kernel(const float *__restrict__ src, const int *__restrict__ rows, const float *__restrict__ w,
                                  const float *__restrict__ b, float eps, float *__restrict__ x_add, T *__restrict__ out, int d) {
     pdl_trigger();
@@ -54,10 +63,18 @@ __global__ void layernorm_kernel(const float *__restrict__ src, const int *__res
     const int r = rows ? rows[i] : i;
     const float *v = src + (size_t)r * d;
     float s = 0.f;
-    for (int c = threadIdx.x; c < d; c += blockDim.x) {
-        const float t = v[c];
-        row_buf[c] = t;
-        s += t;
+    if (VEC) {
+        for (int c = threadIdx.x * 4; c < d; c += blockDim.x * 4) {
+            const float4 t = *reinterpret_cast<const float4 *>(v + c);
+            *reinterpret_cast<float4 *>(row_buf + c) = t;
+            s += (t.x + t.y) + (t.z + t.w);
+        }
+    } else {
+        for (int c = threadIdx.x; c < d; c += blockDim.x) {
+            const float t = v[c];
+            row_buf[c] = t;
+            s += t;
+        }
     }
     const float mean = block_sum(s, scratch) / (float)d;
     float ss = 0.f;
@@ -66,6 +83,24 @@ __global__ void layernorm_kernel(const float *__restrict__ src, const int *__res
         ss += t * t;
     }
     const float inv = 1.f / sqrtf(block_sum(ss, scratch) / (float)d + eps);
+    if (VEC) {
+        for (int c = threadIdx.x * 4; c < d; c += blockDim.x * 4) {
+            const float4 t = *reinterpret_cast<const float4 *>(row_buf + c), ww = *reinterpret_cast<const float4 *>(w + c);
+            const float4 bb = b ? *reinterpret_cast<const float4 *>(b + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+            float4 y = make_float4((t.x - mean) * inv * ww.x + bb.x, (t.y - mean) * inv * ww.y + bb.y,
+                                   (t.z - mean) * inv * ww.z + bb.z, (t.w - mean) * inv * ww.w + bb.w);
+            if (x_add != nullptr) {
+                float *xp = x_add + (size_t)r * d + c;
+                const float4 x = *reinterpret_cast<const float4 *>(xp);
+                y = make_float4(x.x + y.x, x.y + y.y, x.z + y.z, x.w + y.w);
+                *reinterpret_cast<float4 *>(xp) = y;
+                if (out != nullptr) store4_as(out + (size_t)i * d + c, y);
+            } else {
+                store4_as(out + (size_t)i * d + c, y);
+            }
+        }
+        return;
+    }
     for (int c = threadIdx.x; c < d; c += blockDim.x) {
         const float y = (row_buf[c] - mean) * inv * w[c] + (b ? b[c] : 0.f);
         if (x_add != nullptr) {
@@ -86,18 +121,23 @@ JK_EXPORT int jk_layernorm(const float *src, const int *rows, int nrows, int d, 
     JK_REQUIRE(x_add != nullptr || out != nullptr, "layernorm: nothing to write");
     JK_REQUIRE(x_add == nullptr || rows == nullptr, "layernorm: the adding form works on every row");
     JK_REQUIRE((size_t)d * 4 <= 200 * 1024, "layernorm: width %d does not fit shared memory", d);
-    const int threads = d >= 2048 ? 512 : (d >= 512 ? 256 : 128);
+    const bool vec = d % 4 == 0 && ((uintptr_t)src % 16 == 0) && ((uintptr_t)w % 16 == 0) && (b == nullptr || (uintptr_t)b % 16 == 0) &&
+                     (x_add == nullptr || (uintptr_t)x_add % 16 == 0) && (out == nullptr || (uintptr_t)out % 16 == 0);
+    const int threads = d >= 4096 ? 512 : (d >= 1024 ? 256 : 128);
     const size_t smem = (size_t)d * sizeof(float);
+#define LN_LAUNCH(T, VEC)                                                                                                   \
+    do {                                                                                                                    \
+        if (smem > 48 * 1024) cudaFuncSetAttribute(layernorm_kernel<T, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        jk_launch(layernorm_kernel<T, VEC>, dim3(nrows), dim3(threads), smem, stream, src, rows, w, b, eps, x_add, (T *)out, d);   \
+    } while (0)
     if (dtype == JK_F32) {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(layernorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        jk_launch(layernorm_kernel<float>, dim3(nrows), dim3(threads), smem, stream, src, rows, w, b, eps, x_add, (float *)out, d);
+        if (vec) LN_LAUNCH(float, true); else LN_LAUNCH(float, false);
     } else if (dtype == JK_BF16) {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(layernorm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        jk_launch(layernorm_kernel<__nv_bfloat16>, dim3(nrows), dim3(threads), smem, stream, src, rows, w, b, eps, x_add,
-                  (__nv_bfloat16 *)out, d);
+        if (vec) LN_LAUNCH(__nv_bfloat16, true); else LN_LAUNCH(__nv_bfloat16, false);
     } else {
         JK_FAIL(JK_UNSUPPORTED, "layernorm: dtype %d", dtype);
     }
+#undef LN_LAUNCH
     JK_CHECK_LAUNCH("layernorm");
     return JK_OK;
 }
