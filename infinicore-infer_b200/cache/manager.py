@@ -66,8 +66,27 @@ class CacheManager:
         for c, need in enumerate(needs):
             if need is not None and need.group_key() is not None:
                 by_key.setdefault(need.group_key(), []).append(c)
+        from ..kernels.host import max_cache_groups
+        group_need = {key: needs[ids[0]] for key, ids in by_key.items()}
+        if len(by_key) > max_cache_groups():
+            # more kinds of cache than a step carries block tables for (many windows, say): caches that differ only in what
+            # they may give back share a group that keeps pages for the widest of them; every layer still masks by its own
+            merged: Dict[object, List[int]] = {}
+            merged_need: Dict[object, object] = {}
+            for key, ids in by_key.items():
+                need = needs[ids[0]]
+                coarse = next((k for k, other in merged_need.items()
+                               if hasattr(other, "shared_with") and other.shared_with(need) is not None), None)
+                if coarse is None:
+                    merged[key], merged_need[key] = list(ids), need
+                else:
+                    merged[coarse].extend(ids)
+                    merged_need[coarse] = merged_need[coarse].shared_with(need)
+            by_key, group_need = merged, merged_need
+            if len(by_key) > max_cache_groups():
+                raise ValueError(f"the model's layers need {len(by_key)} kinds of paged cache; a step carries block tables for {max_cache_groups()}")
         for gi, (key, ids) in enumerate(by_key.items()):
-            need = needs[ids[0]]
+            need = group_need[key]
             n = (pages_per_group or {}).get(gi, num_pages)
             self.groups.append(need.make_group(ids, n + 1, page_size, self.max_blocks))
             storage = need.make_storage(len(ids), n + 1, page_size, self.slots.num_slots, dtype, device)

@@ -132,3 +132,13 @@ def test_plain_attention_sees_exactly_its_window_and_the_sink_takes_weight():
     assert torch.allclose(o[0, 0, 0], torch.tensor(0.0, dtype=torch.float64))
     assert torch.allclose(o[5, 0, 0], torch.tensor((3 + 4 + 5) / 4.0, dtype=torch.float64))
     assert torch.allclose(o[1, 0, 0], torch.tensor((0 + 1) / 3.0, dtype=torch.float64))
+
+
+def test_more_windows_than_block_tables_share_groups_by_size():
+    from infinicore_infer_b200.cache import CacheManager, PagedKV
+    from infinicore_infer_b200.kernels.host import max_cache_groups
+    n = max_cache_groups() + 3
+    needs = [PagedKV(2, 16, 8 + 4 * i) for i in range(n)] + [PagedKV(1, 32, None, 8)]
+    mgr = CacheManager(needs, num_pages=16, page_size=4, max_requests=2, max_positions=128, device=None)
+    assert len(mgr.groups) == 2 and mgr.groups[0].need.window == 8 + 4 * (n - 1) and mgr.groups[1].need.v_head_dim == 8
+    assert [v.group_index for v in mgr.views] == [0] * n + [1]
