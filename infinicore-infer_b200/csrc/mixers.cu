@@ -99,16 +99,16 @@ __global__ void layernorm_kernel(const float *__restrict__ src, const int *__res
                 store4_as(out + (size_t)i * d + c, y);
             }
         }
-        return;
-    }
-    for (int c = threadIdx.x; c < d; c += blockDim.x) {
-        const float y = (row_buf[c] - mean) * inv * w[c] + (b ? b[c] : 0.f);
-        if (x_add != nullptr) {
-            const float nx = x_add[(size_t)r * d + c] + y;
-            x_add[(size_t)r * d + c] = nx;
-            if (out != nullptr) out[(size_t)i * d + c] = from_f32<T>(nx);
-        } else {
-            out[(size_t)i * d + c] = from_f32<T>(y);
+    } else {
+        for (int c = threadIdx.x; c < d; c += blockDim.x) {
+            const float y = (row_buf[c] - mean) * inv * w[c] + (b ? b[c] : 0.f);
+            if (x_add != nullptr) {
+                const float nx = x_add[(size_t)r * d + c] + y;
+                x_add[(size_t)r * d + c] = nx;
+                if (out != nullptr) out[(size_t)i * d + c] = from_f32<T>(nx);
+            } else {
+                out[(size_t)i * d + c] = from_f32<T>(y);
+            }
         }
     }
 }
@@ -372,7 +372,7 @@ JK_EXPORT int jk_conv_qkv(const float *u, int ld, int q_off, int k_off, int v_of
 // q, k, v pass `qkv_act` (none or silu); q is multiplied by q_scale.  The decay a_t [dk] is either one constant per head
 // (decay[head], for all channels and rows) or projected: z = W2 r_t + b2 with r_t the `rank` columns of the fused
 // product at r_off, a = exp(log_sigmoid(z) / tau), all in float32 (W2 may be stored as bfloat16).
-// A block of the scan kernel owns (head, work item, a slice of value columns) and walks the item's rows in order.  Its 128
+// A block of the scan kernel owns (head, work item, a slice of value columns) and walks the item's rows in order.  Its
 // threads are (column, part): `kq` neighbouring lanes share a column of S, lane `part` keeping the key channels part,
 // part + kq, part + 2 kq ... in registers; a row's output is the lanes' partial sums added by shuffles.  Rows are staged
 // through shared memory a chunk at a time (activations applied, decays formed there, once per block), so a row costs no
@@ -411,12 +411,13 @@ struct ScanArgs {
     const int *piece_reqs;      // [n_piece_reqs, 3] (request, its first piece, its pieces)
     float *piece_state;         // [n_pieces, heads, dk, dv]
     float *cum;                 // [T, heads, dk] running products of a projected decay inside each piece
+    int vec4;                   // 1: rows, offsets and sizes are multiples of four floats: staging moves 16 bytes at a time
 };
 
-constexpr int SCAN_THREADS = 128;
-constexpr int SCAN_CPT = 2;         // columns of S a thread keeps: what it reads of a row's q, k and decay serves both
-
-template <typename TW, int KS>      // KS: key channels per thread
+constexpr int SCAN_THREADS = 256;     // (column pair, part) threads: a row staged once serves 128 columns at four lanes a column
+// SCAN_CPT: columns of S a thread keeps; what it reads of a row's q, k and decay serves them all.  Four where portions run
+// as pieces (the shared-memory reads bound the scan), two in steps of short requests (more blocks, shorter threads).
+template <typename TW, int KS, int SCAN_CPT>      // KS: key channels per thread
 __global__ void __launch_bounds__(SCAN_THREADS)
 linear_scan_kernel(ScanArgs a) {
     pdl_trigger();
@@ -427,7 +428,9 @@ linear_scan_kernel(ScanArgs a) {
     float4 *sx = reinterpret_cast<float4 *>(sm);        // [chunk, dk] (decay, k, q, -) of a row's channel, side by side
     float *sv = sm + 4 * (size_t)a.chunk * dk;          // [chunk, cols]
     float *sr = sv + (size_t)a.chunk * cols;            // [chunk, rank]
-    const int col = threadIdx.x / kq * SCAN_CPT, part = threadIdx.x % kq;
+    // within a warp the column groups vary fastest, so that lanes with one part read neighbouring columns of a state row
+    const int per_warp = 32 / kq, lane = threadIdx.x & 31;
+    const int col = ((threadIdx.x >> 5) * per_warp + lane % per_warp) * SCAN_CPT, part = lane / per_warp;
     bool live[SCAN_CPT];
 #pragma unroll
     for (int c = 0; c < SCAN_CPT; ++c) live[c] = c0 + col + c < a.dv;
@@ -458,26 +461,56 @@ linear_scan_kernel(ScanArgs a) {
                 const int tt = i / a.rank;
                 sr[i] = a.u[(size_t)(t0 + tt) * a.ld + a.r_off + (i - tt * a.rank)];
             }
-        // four elements a thread at a time, their loads ahead of the arithmetic
-        for (int i0 = threadIdx.x; i0 < n * dk; i0 += 4 * SCAN_THREADS) {
-            float qv[4], kv[4];
+        if (a.vec4) {
+            // four neighbouring channels of a row at a time, all of a thread's loads ahead of the arithmetic
+            for (int i0 = threadIdx.x * 4; i0 < n * dk; i0 += 8 * SCAN_THREADS) {
+                float4 qv[2], kv[2];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int i = i0 + j * SCAN_THREADS;
-                if (i < n * dk) {
-                    const int tt = i / dk, kk = i - tt * dk;
-                    const float *row = a.u + (size_t)(t0 + tt) * a.ld;
-                    qv[j] = row[a.q_off + head * dk + kk];
-                    kv[j] = row[a.k_off + head * dk + kk];
+                for (int j = 0; j < 2; ++j) {
+                    const int i = i0 + j * 4 * SCAN_THREADS;
+                    if (i < n * dk) {
+                        const int tt = i / dk, kk = i - tt * dk;
+                        const float *row = a.u + (size_t)(t0 + tt) * a.ld + head * dk + kk;
+                        qv[j] = *reinterpret_cast<const float4 *>(row + a.q_off);
+                        kv[j] = *reinterpret_cast<const float4 *>(row + a.k_off);
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    const int i = i0 + j * 4 * SCAN_THREADS;
+                    if (i < n * dk) {
+                        const float qq[4] = {qv[j].x, qv[j].y, qv[j].z, qv[j].w}, kk4[4] = {kv[j].x, kv[j].y, kv[j].z, kv[j].w};
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            sx[i + e].y = apply_act(a.qkv_act, kk4[e]);
+                            sx[i + e].z = apply_act(a.qkv_act, qq[e]) * a.q_scale;
+                            if (a.w2 == nullptr) sx[i + e].x = head_decay;
+                        }
+                    }
                 }
             }
+        } else {
+            // four elements a thread at a time, their loads ahead of the arithmetic
+            for (int i0 = threadIdx.x; i0 < n * dk; i0 += 4 * SCAN_THREADS) {
+                float qv[4], kv[4];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int i = i0 + j * SCAN_THREADS;
-                if (i < n * dk) {
-                    sx[i].y = apply_act(a.qkv_act, kv[j]);
-                    sx[i].z = apply_act(a.qkv_act, qv[j]) * a.q_scale;
-                    if (a.w2 == nullptr) sx[i].x = head_decay;
+                for (int j = 0; j < 4; ++j) {
+                    const int i = i0 + j * SCAN_THREADS;
+                    if (i < n * dk) {
+                        const int tt = i / dk, kk = i - tt * dk;
+                        const float *row = a.u + (size_t)(t0 + tt) * a.ld;
+                        qv[j] = row[a.q_off + head * dk + kk];
+                        kv[j] = row[a.k_off + head * dk + kk];
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int i = i0 + j * SCAN_THREADS;
+                    if (i < n * dk) {
+                        sx[i].y = apply_act(a.qkv_act, kv[j]);
+                        sx[i].z = apply_act(a.qkv_act, qv[j]) * a.q_scale;
+                        if (a.w2 == nullptr) sx[i].x = head_decay;
+                    }
                 }
             }
         }
@@ -524,7 +557,7 @@ linear_scan_kernel(ScanArgs a) {
 #pragma unroll
             for (int c = 0; c < SCAN_CPT; ++c) {
                 float sum = o[c];
-                for (int off = kq >> 1; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+                for (int off = kq >> 1; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off * per_warp);
                 if (part == 0 && live[c]) a.out[(size_t)(t0 + tt) * a.heads * a.dv + head * a.dv + c0 + col + c] = sum;
             }
         }
@@ -591,28 +624,43 @@ __global__ void scan_carry_kernel(ScanArgs a) {
     *slot = run;
 }
 
-// out[t, head, v] += sum_k q_t[k] b_t[k] S_start[k, v] for the rows of a piece.  A block owns (piece, head, 64 columns):
+// out[t, head, v] += sum_k q_t[k] b_t[k] S_start[k, v] for the rows of a piece.  A block owns (piece, head, 128 columns):
 // S_start's slice in shared memory, 16 rows of q * b at a time beside it (transposed, so that a thread reads the eight rows
-// it works on as two vectors); thread (half, column) adds up eight rows against its column.
-constexpr int PFX_COLS = 64, PFX_ROWS = 16, PFX_K = 128;
+// it works on as two vectors); thread (half, column pair) adds up eight rows against its two columns.
+constexpr int PFX_COLS = 128, PFX_ROWS = 16, PFX_K = 128;
+constexpr size_t PFX_SMEM = sizeof(float) * (PFX_K * PFX_COLS + PFX_K * PFX_ROWS);
 
 __global__ void __launch_bounds__(128)
 scan_prefix_kernel(ScanArgs a) {
     pdl_trigger();
     pdl_wait();
-    __shared__ __align__(16) float Ssm[PFX_K * PFX_COLS];
-    __shared__ __align__(16) float qb[PFX_K * PFX_ROWS];
+    extern __shared__ __align__(16) float pfx_sm[];
+    float *Ssm = pfx_sm;                        // [PFX_K, PFX_COLS]
+    float *qb = pfx_sm + PFX_K * PFX_COLS;      // [PFX_K, PFX_ROWS]
+    __shared__ float pw[SCAN_PIECE];            // a constant decay to the powers 1 .. SCAN_PIECE, by the carry's own products
     const int p = blockIdx.x, head = blockIdx.y, c0 = blockIdx.z * PFX_COLS;
     const int first = a.pieces[2 * p], n = a.pieces[2 * p + 1];
-    const int v = threadIdx.x % PFX_COLS, half = threadIdx.x / PFX_COLS;
+    const int v = (threadIdx.x % 64) * 2, half = threadIdx.x / 64;
     const float *S = a.piece_state + ((size_t)p * a.heads + head) * a.dk * a.dv;
-    const float hd = a.decay ? a.decay[head] : 1.f;
+    if (a.w2 == nullptr && threadIdx.x < SCAN_PIECE) {
+        const float hd = a.decay[head];
+        float b = hd;
+        for (int j = 0; j < threadIdx.x; ++j) b *= hd;
+        pw[threadIdx.x] = b;
+    }
     for (int k0 = 0; k0 < a.dk; k0 += PFX_K) {
         const int nk = min(PFX_K, a.dk - k0);
         __syncthreads();
-        for (int i = threadIdx.x; i < nk * PFX_COLS; i += 128) {
-            const int kk = i / PFX_COLS, cc = i - kk * PFX_COLS;
-            Ssm[i] = c0 + cc < a.dv ? S[(size_t)(k0 + kk) * a.dv + c0 + cc] : 0.f;
+        if (a.vec4 && c0 + PFX_COLS <= a.dv) {
+            for (int i = threadIdx.x * 4; i < nk * PFX_COLS; i += 128 * 4) {
+                const int kk = i / PFX_COLS, cc = i - kk * PFX_COLS;
+                *reinterpret_cast<float4 *>(Ssm + i) = *reinterpret_cast<const float4 *>(S + (size_t)(k0 + kk) * a.dv + c0 + cc);
+            }
+        } else {
+            for (int i = threadIdx.x; i < nk * PFX_COLS; i += 128) {
+                const int kk = i / PFX_COLS, cc = i - kk * PFX_COLS;
+                Ssm[i] = c0 + cc < a.dv ? S[(size_t)(k0 + kk) * a.dv + c0 + cc] : 0.f;
+            }
         }
         for (int t0 = 0; t0 < n; t0 += PFX_ROWS) {
             const int nt = min(PFX_ROWS, n - t0);
@@ -622,33 +670,33 @@ scan_prefix_kernel(ScanArgs a) {
                 float val = 0.f;
                 if (tt < nt) {
                     const int t = first + t0 + tt;
-                    float b;
-                    if (a.w2 != nullptr) {
-                        b = a.cum[((size_t)t * a.heads + head) * a.dk + k0 + kk];
-                    } else {
-                        b = hd;
-                        for (int j = 0; j < t0 + tt; ++j) b *= hd;       // the same products, in the same order, as the carry's
-                    }
+                    const float b = a.w2 != nullptr ? a.cum[((size_t)t * a.heads + head) * a.dk + k0 + kk] : pw[t0 + tt];
                     val = apply_act(a.qkv_act, a.u[(size_t)t * a.ld + a.q_off + head * a.dk + k0 + kk]) * a.q_scale * b;
                 }
                 qb[kk * PFX_ROWS + tt] = val;
             }
             __syncthreads();
-            float acc[8];
+            float acc[2][8];
 #pragma unroll
-            for (int r = 0; r < 8; ++r) acc[r] = 0.f;
+            for (int r = 0; r < 8; ++r) acc[0][r] = acc[1][r] = 0.f;
             for (int kk = 0; kk < nk; ++kk) {
-                const float sv = Ssm[kk * PFX_COLS + v];
+                const float2 sv = *reinterpret_cast<const float2 *>(Ssm + kk * PFX_COLS + v);
                 const float4 x = *reinterpret_cast<const float4 *>(qb + kk * PFX_ROWS + half * 8);
                 const float4 y = *reinterpret_cast<const float4 *>(qb + kk * PFX_ROWS + half * 8 + 4);
-                acc[0] = fmaf(x.x, sv, acc[0]); acc[1] = fmaf(x.y, sv, acc[1]); acc[2] = fmaf(x.z, sv, acc[2]); acc[3] = fmaf(x.w, sv, acc[3]);
-                acc[4] = fmaf(y.x, sv, acc[4]); acc[5] = fmaf(y.y, sv, acc[5]); acc[6] = fmaf(y.z, sv, acc[6]); acc[7] = fmaf(y.w, sv, acc[7]);
-            }
-            if (c0 + v < a.dv) {
+                const float rowv[8] = {x.x, x.y, x.z, x.w, y.x, y.y, y.z, y.w};
 #pragma unroll
                 for (int r = 0; r < 8; ++r) {
-                    const int tt = half * 8 + r;
-                    if (tt < nt) a.out[(size_t)(first + t0 + tt) * a.heads * a.dv + head * a.dv + c0 + v] += acc[r];
+                    acc[0][r] = fmaf(rowv[r], sv.x, acc[0][r]);
+                    acc[1][r] = fmaf(rowv[r], sv.y, acc[1][r]);
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {
+                const int tt = half * 8 + r;
+                if (tt < nt) {
+                    float *o = a.out + (size_t)(first + t0 + tt) * a.heads * a.dv + head * a.dv + c0 + v;
+                    if (c0 + v < a.dv) o[0] += acc[0][r];
+                    if (c0 + v + 1 < a.dv) o[1] += acc[1][r];
                 }
             }
         }
@@ -677,27 +725,33 @@ JK_EXPORT int jk_linear_scan(const float *u, int ld, int q_off, int k_off, int v
     const long long state_floats = (long long)n_pieces * heads * dk * dv;
     JK_REQUIRE(n_pieces == 0 || state_floats + (w2 ? (long long)T * heads * dk : 0) <= scratch_floats,
                "linear_scan: %d pieces need more scratch than %lld floats", n_pieces, scratch_floats);
-    // lanes per column: as few as keep a thread's share of a column at 32 channels (64 beyond 1024 channels); more of them,
+    // lanes per column: as few as keep a thread's state at 64 values (more beyond 1024 and 512 channels); more of them,
     // and so fewer columns a block and more blocks, while the blocks do not fill the SMs
     const int sm_count = sms > 0 ? sms : 148;
     const int items = n_direct + n_pieces;
+    const int cpt = n_pieces > 0 ? 4 : 2;
     int kq = 1;
-    while (kq < 32 && (dk + kq - 1) / kq > 32) kq *= 2;
-    while (kq < 32 && 2 * kq <= dk &&
-           (long long)heads * items * ((dv + SCAN_THREADS / kq * SCAN_CPT - 1) / (SCAN_THREADS / kq * SCAN_CPT)) < sm_count)
+    while (kq < 32 && (dk + kq - 1) / kq > 64 / cpt) kq *= 2;
+    while (kq < 32 && 2 * kq <= dk && (long long)heads * items * ((dv + SCAN_THREADS / kq * cpt - 1) / (SCAN_THREADS / kq * cpt)) < sm_count)
         kq *= 2;
-    const int cols = SCAN_THREADS / kq * SCAN_CPT;
+    const int cols = SCAN_THREADS / kq * cpt;
     const int per_thread = (dk + kq - 1) / kq;
     const size_t row_bytes = sizeof(float) * (4 * (size_t)dk + cols + (w2 ? rank : 0));
     int chunk = (int)std::min<size_t>(32, std::max<size_t>(1, (40 * 1024) / row_bytes));
     chunk = std::min(chunk, T);
     ScanArgs a{u, ld, q_off, k_off, v_off, r_off, heads, dk, dv, qkv_act, q_scale, decay, w2, b2, rank, tau > 0.f ? 1.f / tau : 0.f,
                state, req_start, slot_ids, out, kq, chunk, direct, n_direct, pieces, n_pieces, piece_reqs, scratch,
-               scratch ? scratch + state_floats : nullptr};
+               scratch ? scratch + state_floats : nullptr,
+               (dk % 4 == 0 && dv % 4 == 0 && ld % 4 == 0 && q_off % 4 == 0 && k_off % 4 == 0 && (uintptr_t)u % 16 == 0 &&
+                (scratch == nullptr || (uintptr_t)scratch % 16 == 0)) ? 1 : 0};
     dim3 grid(heads, items, (dv + cols - 1) / cols);
     JK_REQUIRE(items <= 65535 && grid.z <= 65535 && heads <= 65535, "linear_scan: %d items in one launch", items);
     const size_t smem = row_bytes * chunk;
-#define SCAN_LAUNCH(TW, KS) jk_launch(linear_scan_kernel<TW, KS>, grid, dim3(SCAN_THREADS), smem, stream, a)
+#define SCAN_LAUNCH(TW, KS)                                                                                         \
+    do {                                                                                                            \
+        if (cpt == 4) jk_launch(linear_scan_kernel<TW, KS, 4>, grid, dim3(SCAN_THREADS), smem, stream, a);          \
+        else jk_launch(linear_scan_kernel<TW, KS, 2>, grid, dim3(SCAN_THREADS), smem, stream, a);                   \
+    } while (0)
 #define SCAN_LAUNCH_T(TW)                                   \
     do {                                                    \
         if (per_thread <= 1) SCAN_LAUNCH(TW, 1);            \
@@ -716,7 +770,8 @@ JK_EXPORT int jk_linear_scan(const float *u, int ld, int q_off, int k_off, int v
     if (n_pieces > 0) {
         jk_launch(scan_carry_kernel, dim3((dk * dv + 255) / 256, heads, n_piece_reqs), dim3(256), 0, stream, a);
         JK_CHECK_LAUNCH("scan_carry");
-        jk_launch(scan_prefix_kernel, dim3(n_pieces, heads, (dv + PFX_COLS - 1) / PFX_COLS), dim3(128), 0, stream, a);
+        cudaFuncSetAttribute(scan_prefix_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PFX_SMEM);
+        jk_launch(scan_prefix_kernel, dim3(n_pieces, heads, (dv + PFX_COLS - 1) / PFX_COLS), dim3(128), PFX_SMEM, stream, a);
         JK_CHECK_LAUNCH("scan_prefix");
     }
     return JK_OK;
