@@ -346,7 +346,9 @@ JK_EXPORT int jk_conv_qkv(const float *u, int ld, int q_off, int k_off, int v_of
     const int C = a.nq + a.nk + a.nv;
     const size_t smem = (size_t)C * sizeof(float);
     JK_REQUIRE(smem <= 200 * 1024, "conv_qkv: %d channels do not fit shared memory", C);
-    const int threads = C >= 2048 ? 512 : (C >= 512 ? 256 : 128);
+    // a step of few rows has few blocks: more threads a row then, so that a thread's chain of channels is short
+    int threads = C >= 2048 ? 512 : (C >= 512 ? 256 : 128);
+    if (T <= 64) threads = std::min(1024, std::max(threads, (C / 2 + 31) / 32 * 32));
     if (dtype == JK_F32) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(conv_qkv_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         jk_launch(conv_qkv_kernel<float>, dim3(T), dim3(threads), smem, stream, a);
