@@ -414,6 +414,8 @@ struct ScanArgs {
     float *piece_state;         // [n_pieces, heads, dk, dv]
     float *cum;                 // [T, heads, dk] running products of a projected decay inside each piece
     int vec4;                   // 1: rows, offsets and sizes are multiples of four floats: staging moves 16 bytes at a time
+    int dkp;                    // channels of a staged row: dk rounded up to kq * KS; the padding stays zero, so the scan's
+                                // inner loop needs no bounds
 };
 
 constexpr int SCAN_THREADS = 256;     // (column pair, part) threads: a row staged once serves 128 columns at four lanes a column
@@ -427,8 +429,9 @@ linear_scan_kernel(ScanArgs a) {
     extern __shared__ __align__(16) float sm[];
     const int kq = a.kq, cols = SCAN_THREADS / kq * SCAN_CPT, dk = a.dk;
     const int head = blockIdx.x, item = blockIdx.y, c0 = blockIdx.z * cols;
-    float4 *sx = reinterpret_cast<float4 *>(sm);        // [chunk, dk] (decay, k, q, -) of a row's channel, side by side
-    float *sv = sm + 4 * (size_t)a.chunk * dk;          // [chunk, cols]
+    const int dkp = a.dkp;
+    float4 *sx = reinterpret_cast<float4 *>(sm);        // [chunk, dkp] (decay, k, q, -) of a row's channel, side by side
+    float *sv = sm + 4 * (size_t)a.chunk * dkp;         // [chunk, cols]
     float *sr = sv + (size_t)a.chunk * cols;            // [chunk, rank]
     // within a warp the column groups vary fastest, so that lanes with one part read neighbouring columns of a state row
     const int per_warp = 32 / kq, lane = threadIdx.x & 31;
@@ -455,6 +458,8 @@ linear_scan_kernel(ScanArgs a) {
         for (int i = 0; i < KS; ++i) s[c][i] = (!piece && live[c] && part + i * kq < dk) ? S[(size_t)(part + i * kq) * a.dv + c] : 0.f;
     const float head_decay = a.decay ? a.decay[head] : 1.f;
     const bool write_cum = piece && a.w2 != nullptr && blockIdx.z == 0;
+    if (dkp > dk)       // the padding channels: zero once, nothing writes them afterwards
+        for (int i = threadIdx.x; i < a.chunk * dkp; i += SCAN_THREADS) sx[i] = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int t0 = first; t0 < last; t0 += a.chunk) {
         const int n = min(a.chunk, last - t0);
         __syncthreads();            // the chunk before has been read
@@ -482,11 +487,12 @@ linear_scan_kernel(ScanArgs a) {
                     const int i = i0 + j * 4 * SCAN_THREADS;
                     if (i < n * dk) {
                         const float qq[4] = {qv[j].x, qv[j].y, qv[j].z, qv[j].w}, kk4[4] = {kv[j].x, kv[j].y, kv[j].z, kv[j].w};
+                        const int at = (i / dk) * dkp + i % dk;
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
-                            sx[i + e].y = apply_act(a.qkv_act, kk4[e]);
-                            sx[i + e].z = apply_act(a.qkv_act, qq[e]) * a.q_scale;
-                            if (a.w2 == nullptr) sx[i + e].x = head_decay;
+                            sx[at + e].y = apply_act(a.qkv_act, kk4[e]);
+                            sx[at + e].z = apply_act(a.qkv_act, qq[e]) * a.q_scale;
+                            if (a.w2 == nullptr) sx[at + e].x = head_decay;
                         }
                     }
                 }
@@ -509,9 +515,10 @@ linear_scan_kernel(ScanArgs a) {
                 for (int j = 0; j < 4; ++j) {
                     const int i = i0 + j * SCAN_THREADS;
                     if (i < n * dk) {
-                        sx[i].y = apply_act(a.qkv_act, kv[j]);
-                        sx[i].z = apply_act(a.qkv_act, qv[j]) * a.q_scale;
-                        if (a.w2 == nullptr) sx[i].x = head_decay;
+                        const int at = (i / dk) * dkp + i % dk;
+                        sx[at].y = apply_act(a.qkv_act, kv[j]);
+                        sx[at].z = apply_act(a.qkv_act, qv[j]) * a.q_scale;
+                        if (a.w2 == nullptr) sx[at].x = head_decay;
                     }
                 }
             }
@@ -527,7 +534,7 @@ linear_scan_kernel(ScanArgs a) {
                 const TW *w = (const TW *)a.w2 + (size_t)(head * dk + kk) * a.rank;
                 float z = a.b2 ? a.b2[head * dk + kk] : 0.f;
                 for (int r = 0; r < a.rank; ++r) z = fmaf(to_f32(w[r]), sr[tt * a.rank + r], z);
-                sx[i].x = expf(log_sigmoid_f(z) * a.inv_tau);
+                sx[tt * dkp + kk].x = expf(log_sigmoid_f(z) * a.inv_tau);
             }
             __syncthreads();
         }
@@ -535,30 +542,28 @@ linear_scan_kernel(ScanArgs a) {
             for (int kk = threadIdx.x; kk < dk; kk += SCAN_THREADS) {
                 float b = t0 > first ? a.cum[((size_t)(t0 - 1) * a.heads + head) * dk + kk] : 1.f;
                 for (int tt = 0; tt < n; ++tt) {
-                    b *= sx[tt * dk + kk].x;
+                    b *= sx[tt * dkp + kk].x;
                     a.cum[((size_t)(t0 + tt) * a.heads + head) * dk + kk] = b;
                 }
             }
         }
         for (int tt = 0; tt < n; ++tt) {
-            float vv[SCAN_CPT], o[SCAN_CPT];
+            float vv[SCAN_CPT], o[SCAN_CPT][2];
 #pragma unroll
-            for (int c = 0; c < SCAN_CPT; ++c) { vv[c] = sv[tt * cols + col + c]; o[c] = 0.f; }
-            const float4 *x = sx + (size_t)tt * dk + part;
+            for (int c = 0; c < SCAN_CPT; ++c) { vv[c] = sv[tt * cols + col + c]; o[c][0] = o[c][1] = 0.f; }
+            const float4 *x = sx + (size_t)tt * dkp + part;
 #pragma unroll
-            for (int i = 0; i < KS; ++i) {
-                if (part + i * kq < dk) {
-                    const float4 e = x[i * kq];
+            for (int i = 0; i < KS; ++i) {          // no bounds: a staged row is padded with zeros up to kq * KS channels
+                const float4 e = x[i * kq];
 #pragma unroll
-                    for (int c = 0; c < SCAN_CPT; ++c) {
-                        s[c][i] = fmaf(e.x, s[c][i], e.y * vv[c]);
-                        o[c] = fmaf(s[c][i], e.z, o[c]);
-                    }
+                for (int c = 0; c < SCAN_CPT; ++c) {
+                    s[c][i] = fmaf(e.x, s[c][i], e.y * vv[c]);
+                    o[c][i & 1] = fmaf(s[c][i], e.z, o[c][i & 1]);
                 }
             }
 #pragma unroll
             for (int c = 0; c < SCAN_CPT; ++c) {
-                float sum = o[c];
+                float sum = o[c][0] + o[c][1];
                 for (int off = kq >> 1; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off * per_warp);
                 if (part == 0 && live[c]) a.out[(size_t)(t0 + tt) * a.heads * a.dv + head * a.dv + c0 + col + c] = sum;
             }
@@ -626,11 +631,14 @@ __global__ void scan_carry_kernel(ScanArgs a) {
     *slot = run;
 }
 
-// out[t, head, v] += sum_k q_t[k] b_t[k] S_start[k, v] for the rows of a piece.  A block owns (piece, head, 128 columns):
-// S_start's slice in shared memory, 16 rows of q * b at a time beside it (transposed, so that a thread reads the eight rows
-// it works on as two vectors); thread (half, column pair) adds up eight rows against its two columns.
-constexpr int PFX_COLS = 128, PFX_ROWS = 16, PFX_K = 128;
+// out[t, head, v] += sum_k q_t[k] b_t[k] S_start[k, v] for the rows of a piece: a float32 product of [rows, dk] by
+// [dk, dv] per piece and head.  A block owns (piece, head, 128 columns): S_start's slice and the piece's rows of q * b
+// (transposed) lie in shared memory; thread (ty, tx) of 8 x 16 keeps an 8 x 8 tile of the result in registers (rows
+// ty * 4 + {0..3} and 32 + ty * 4 + {0..3}, columns tx * 4 + {0..3} and 64 + tx * 4 + {0..3}), so that a step of k costs
+// four 16-byte reads for 64 products.
+constexpr int PFX_COLS = 128, PFX_ROWS = SCAN_PIECE, PFX_K = 128;
 constexpr size_t PFX_SMEM = sizeof(float) * (PFX_K * PFX_COLS + PFX_K * PFX_ROWS);
+static_assert(PFX_ROWS == 64, "the prefix kernel's tiles are written for pieces of 64 rows");
 
 __global__ void __launch_bounds__(128)
 scan_prefix_kernel(ScanArgs a) {
@@ -642,7 +650,7 @@ scan_prefix_kernel(ScanArgs a) {
     __shared__ float pw[SCAN_PIECE];            // a constant decay to the powers 1 .. SCAN_PIECE, by the carry's own products
     const int p = blockIdx.x, head = blockIdx.y, c0 = blockIdx.z * PFX_COLS;
     const int first = a.pieces[2 * p], n = a.pieces[2 * p + 1];
-    const int v = (threadIdx.x % 64) * 2, half = threadIdx.x / 64;
+    const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
     const float *S = a.piece_state + ((size_t)p * a.heads + head) * a.dk * a.dv;
     if (a.w2 == nullptr && threadIdx.x < SCAN_PIECE) {
         const float hd = a.decay[head];
@@ -650,6 +658,11 @@ scan_prefix_kernel(ScanArgs a) {
         for (int j = 0; j < threadIdx.x; ++j) b *= hd;
         pw[threadIdx.x] = b;
     }
+    float acc[8][8];
+#pragma unroll
+    for (int r = 0; r < 8; ++r)
+#pragma unroll
+        for (int c = 0; c < 8; ++c) acc[r][c] = 0.f;
     for (int k0 = 0; k0 < a.dk; k0 += PFX_K) {
         const int nk = min(PFX_K, a.dk - k0);
         __syncthreads();
@@ -664,43 +677,40 @@ scan_prefix_kernel(ScanArgs a) {
                 Ssm[i] = c0 + cc < a.dv ? S[(size_t)(k0 + kk) * a.dv + c0 + cc] : 0.f;
             }
         }
-        for (int t0 = 0; t0 < n; t0 += PFX_ROWS) {
-            const int nt = min(PFX_ROWS, n - t0);
-            __syncthreads();
-            for (int i = threadIdx.x; i < PFX_ROWS * nk; i += 128) {
-                const int tt = i / nk, kk = i - tt * nk;
-                float val = 0.f;
-                if (tt < nt) {
-                    const int t = first + t0 + tt;
-                    const float b = a.w2 != nullptr ? a.cum[((size_t)t * a.heads + head) * a.dk + k0 + kk] : pw[t0 + tt];
-                    val = apply_act(a.qkv_act, a.u[(size_t)t * a.ld + a.q_off + head * a.dk + k0 + kk]) * a.q_scale * b;
-                }
-                qb[kk * PFX_ROWS + tt] = val;
+        // q * b of the piece's rows, transposed; rows beyond the piece's end are zeros
+        for (int i = threadIdx.x; i < PFX_ROWS * nk; i += 128) {
+            const int tt = i / nk, kk = i - tt * nk;
+            float val = 0.f;
+            if (tt < n) {
+                const int t = first + tt;
+                const float b = a.w2 != nullptr ? a.cum[((size_t)t * a.heads + head) * a.dk + k0 + kk] : pw[tt];
+                val = apply_act(a.qkv_act, a.u[(size_t)t * a.ld + a.q_off + head * a.dk + k0 + kk]) * a.q_scale * b;
             }
-            __syncthreads();
-            float acc[2][8];
+            qb[kk * PFX_ROWS + tt] = val;
+        }
+        __syncthreads();
+        for (int kk = 0; kk < nk; ++kk) {
+            const float4 r0 = *reinterpret_cast<const float4 *>(qb + kk * PFX_ROWS + ty * 4);
+            const float4 r1 = *reinterpret_cast<const float4 *>(qb + kk * PFX_ROWS + 32 + ty * 4);
+            const float4 s0 = *reinterpret_cast<const float4 *>(Ssm + kk * PFX_COLS + tx * 4);
+            const float4 s1 = *reinterpret_cast<const float4 *>(Ssm + kk * PFX_COLS + 64 + tx * 4);
+            const float rv[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+            const float cv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
 #pragma unroll
-            for (int r = 0; r < 8; ++r) acc[0][r] = acc[1][r] = 0.f;
-            for (int kk = 0; kk < nk; ++kk) {
-                const float2 sv = *reinterpret_cast<const float2 *>(Ssm + kk * PFX_COLS + v);
-                const float4 x = *reinterpret_cast<const float4 *>(qb + kk * PFX_ROWS + half * 8);
-                const float4 y = *reinterpret_cast<const float4 *>(qb + kk * PFX_ROWS + half * 8 + 4);
-                const float rowv[8] = {x.x, x.y, x.z, x.w, y.x, y.y, y.z, y.w};
+            for (int r = 0; r < 8; ++r)
 #pragma unroll
-                for (int r = 0; r < 8; ++r) {
-                    acc[0][r] = fmaf(rowv[r], sv.x, acc[0][r]);
-                    acc[1][r] = fmaf(rowv[r], sv.y, acc[1][r]);
-                }
-            }
+                for (int c = 0; c < 8; ++c) acc[r][c] = fmaf(rv[r], cv[c], acc[r][c]);
+        }
+    }
 #pragma unroll
-            for (int r = 0; r < 8; ++r) {
-                const int tt = half * 8 + r;
-                if (tt < nt) {
-                    float *o = a.out + (size_t)(first + t0 + tt) * a.heads * a.dv + head * a.dv + c0 + v;
-                    if (c0 + v < a.dv) o[0] += acc[0][r];
-                    if (c0 + v + 1 < a.dv) o[1] += acc[1][r];
-                }
-            }
+    for (int r = 0; r < 8; ++r) {
+        const int tt = (r < 4 ? 0 : 32) + ty * 4 + (r & 3);
+        if (tt >= n) continue;
+        float *o = a.out + (size_t)(first + tt) * a.heads * a.dv + head * a.dv + c0;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            const int cc = (c < 4 ? 0 : 64) + tx * 4 + (c & 3);
+            if (c0 + cc < a.dv) o[cc] += acc[r][c];
         }
     }
 }
@@ -738,14 +748,18 @@ JK_EXPORT int jk_linear_scan(const float *u, int ld, int q_off, int k_off, int v
         kq *= 2;
     const int cols = SCAN_THREADS / kq * cpt;
     const int per_thread = (dk + kq - 1) / kq;
-    const size_t row_bytes = sizeof(float) * (4 * (size_t)dk + cols + (w2 ? rank : 0));
+    int ks = 1;
+    while (ks < per_thread) ks *= 2;            // the instance's channels a thread (below)
+    const int dkp = kq * ks;
+    const size_t row_bytes = sizeof(float) * (4 * (size_t)dkp + cols + (w2 ? rank : 0));
     int chunk = (int)std::min<size_t>(32, std::max<size_t>(1, (40 * 1024) / row_bytes));
     chunk = std::min(chunk, T);
     ScanArgs a{u, ld, q_off, k_off, v_off, r_off, heads, dk, dv, qkv_act, q_scale, decay, w2, b2, rank, tau > 0.f ? 1.f / tau : 0.f,
                state, req_start, slot_ids, out, kq, chunk, direct, n_direct, pieces, n_pieces, piece_reqs, scratch,
                scratch ? scratch + state_floats : nullptr,
                (dk % 4 == 0 && dv % 4 == 0 && ld % 4 == 0 && q_off % 4 == 0 && k_off % 4 == 0 && (uintptr_t)u % 16 == 0 &&
-                (scratch == nullptr || (uintptr_t)scratch % 16 == 0)) ? 1 : 0};
+                (scratch == nullptr || (uintptr_t)scratch % 16 == 0)) ? 1 : 0,
+               dkp};
     dim3 grid(heads, items, (dv + cols - 1) / cols);
     JK_REQUIRE(items <= 65535 && grid.z <= 65535 && heads <= 65535, "linear_scan: %d items in one launch", items);
     const size_t smem = row_bytes * chunk;
