@@ -169,7 +169,7 @@ def test_sink_and_gate_in_the_legacy_tensor_core_tiles(folders):
 @pytest.mark.parametrize("dtype", list(DTYPES))
 def test_every_token_decoded_alone_through_graphs(folders, engines, dtype):
     """Long decoding: every token a step of its own, so windows, pages and tails are passed one position at a time."""
-    for name in ("mixed-a", "mixed-b"):
+    for name in ("mixed-a", "mixed-b", "heads64", "heads32", "heads128"):       # the last three: the split-key decode kernels
         toks, want = expected(folders, name, 77, 140)
         eng = engines(name, dtype)
         check(run(eng, tail_decode("r", toks, tail=len(toks))), "r", want, TOL[dtype], f"{name} {dtype} token by token")
