@@ -51,6 +51,7 @@ class PagedKV(CacheNeed):
     head_dim: int
     window: Optional[int] = None      # None: all keys are kept
     v_head_dim: Optional[int] = None  # None: as head_dim
+    values_in_keys: bool = False      # True: a value is the leading v_head_dim elements of its key; no pages of its own
 
     def group_key(self):
         return self
@@ -60,11 +61,11 @@ class PagedKV(CacheNeed):
         kept for the wider of the two windows.  None if the two cannot share (other sizes, another kind of need)."""
         if not isinstance(other, PagedKV):
             return None
-        if (self.num_kv_heads, self.head_dim, self.v_head_dim or self.head_dim) != \
-                (other.num_kv_heads, other.head_dim, other.v_head_dim or other.head_dim):
+        if (self.num_kv_heads, self.head_dim, self.v_head_dim or self.head_dim, self.values_in_keys) != \
+                (other.num_kv_heads, other.head_dim, other.v_head_dim or other.head_dim, other.values_in_keys):
             return None
         window = None if self.window is None or other.window is None else max(self.window, other.window)
-        return PagedKV(self.num_kv_heads, self.head_dim, window, self.v_head_dim)
+        return PagedKV(self.num_kv_heads, self.head_dim, window, self.v_head_dim, self.values_in_keys)
 
     def make_group(self, cache_ids, num_pages: int, page_size: int, max_blocks: int) -> "CacheGroup":
         return CacheGroup(self, cache_ids, num_pages, page_size, max_blocks=max_blocks)
@@ -76,7 +77,8 @@ class PagedKV(CacheNeed):
         shape = (count, num_pages, self.num_kv_heads, page_size, self.head_dim)
         v_shape = shape[:-1] + (self.v_head_dim or self.head_dim,)
         # zeros: what lies beyond a request's last position in a held page must be finite for every kernel
-        return torch.zeros(shape, dtype=dtype, device=device), torch.zeros(v_shape, dtype=dtype, device=device)
+        keys = torch.zeros(shape, dtype=dtype, device=device)
+        return keys, (keys if self.values_in_keys else torch.zeros(v_shape, dtype=dtype, device=device))
 
     def make_view(self, storage, index: int, group_index: int, page_size: int):
         from .manager import KVView

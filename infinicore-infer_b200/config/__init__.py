@@ -1,8 +1,10 @@
 """Configuration: typed specifications, the MiniCPM/FM9G config, the architecture registry."""
-from .specs import (AttentionSpec, BlockSpec, ConfigError, ConvAttentionSpec, GLUSpec, LayerNormSpec, LinearAttentionSpec,
-                    ModelSpec, PairRotarySpec, PostNormBlockSpec, RMSNormSpec, RopeSpec, RunEntry, SwiGLUSpec, default_order)
+from .specs import (AttentionSpec, BlockSpec, ConfigError, ConvAttentionSpec, FrequencyRampSpec, GLUSpec, LatentAttentionSpec,
+                    LayerNormSpec, LinearAttentionSpec, ModelSpec, PairRotarySpec, PostNormBlockSpec, ReinjectSpec, RMSNormSpec,
+                    RopeSpec, RoutedExpertsSpec, RunEntry, SandwichBlockSpec, SelectiveScanSpec, SwiGLUSpec, default_order)
 from .minicpm import MiniCPMConfig
 from .sitelorn import SitelornConfig
+from .vunelix import VunelixConfig
 from .presets import PRESETS, Preset
 from .registry import (architecture_names, config_class_for, read_config,
                        register_architecture)
@@ -12,8 +14,10 @@ for _name in ("minicpm", "fm9g", "llama", "MiniCPMForCausalLM", "LlamaForCausalL
     register_architecture(_name, MiniCPMConfig)
 
 register_architecture("sitelorn", SitelornConfig)
+register_architecture("vunelix", VunelixConfig)
 
 __all__ = [
+    "FrequencyRampSpec", "LatentAttentionSpec", "ReinjectSpec", "RoutedExpertsSpec", "SandwichBlockSpec", "SelectiveScanSpec", "VunelixConfig",
     "ConvAttentionSpec", "GLUSpec", "LayerNormSpec", "LinearAttentionSpec", "PairRotarySpec", "PostNormBlockSpec", "SitelornConfig",
     "AttentionSpec", "BlockSpec", "ConfigError", "ModelSpec", "RMSNormSpec", "RopeSpec",
     "RunEntry", "SwiGLUSpec", "default_order", "MiniCPMConfig", "architecture_names",

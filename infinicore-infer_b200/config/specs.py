@@ -21,9 +21,11 @@ class ConfigError(ValueError):
 
 @dataclass(frozen=True)
 class RMSNormSpec:
-    """y = x * w / sqrt(mean(x^2) + eps)  (reference: src/models/jiuge/jiuge.cpp:198)."""
+    """y = x * w / sqrt(mean(x^2) + eps)  (reference: src/models/jiuge/jiuge.cpp:198).  ``weight_name`` is appended to the
+    part's prefix."""
     size: int
     eps: float
+    weight_name: str = "weight"
     kind: str = "rmsnorm"
 
 
@@ -82,12 +84,40 @@ class LayerNormSpec:
 
 
 @dataclass(frozen=True)
+class FrequencyRampSpec:
+    """Stretching of a rotation for sequences longer than ``original`` positions: pair i keeps its frequency f_i where its
+    wavelength fits more than ``fast`` times into ``original``, gets f_i / ``factor`` where it fits fewer than ``slow`` times,
+    and a mixture between: with where(t) = dims ln(original / (2 pi t)) / (2 ln base), lo = max(floor(where(fast)), 0),
+    hi = min(ceil(where(slow)), dims - 1), ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), the frequency is
+    f_i / factor * ramp_i + f_i (1 - ramp_i).  Cos and sin are multiplied by ``magnitude_slope`` ln(factor) + 1."""
+    factor: float
+    original: float
+    fast: float
+    slow: float
+    magnitude_slope: float = 0.1
+
+
+@dataclass(frozen=True)
 class PairRotarySpec:
     """Rotation of the first ``dims`` elements of a head in pairs (2i, 2i+1) by the angle ``p * base ** (-2i / dims)``,
-    formed in float32 from the position; the other elements pass unchanged.  Needs no table and no longest position."""
+    formed in float32 from the position; the other elements pass unchanged.  Needs no table and no longest position.
+    ``scaling`` stretches the frequencies (``FrequencyRampSpec``)."""
     dims: int
     base: float
+    scaling: Optional[FrequencyRampSpec] = None
     kind: str = "pair_rotary"
+
+    def frequencies(self):
+        """(f_i for i < dims / 2 in float64, the factor of cos and sin)."""
+        import math
+        f = [float(self.base) ** (-2.0 * i / self.dims) for i in range(self.dims // 2)]
+        s = self.scaling
+        if s is None:
+            return f, 1.0
+        where = lambda turns: self.dims * math.log(s.original / (2.0 * math.pi * turns)) / (2.0 * math.log(self.base))
+        lo, hi = max(math.floor(where(s.fast)), 0), min(math.ceil(where(s.slow)), self.dims - 1)
+        ramp = [min(max((i - lo) / max(hi - lo, 0.001), 0.0), 1.0) for i in range(self.dims // 2)]
+        return [fi / s.factor * r + fi * (1.0 - r) for fi, r in zip(f, ramp)], s.magnitude_slope * math.log(s.factor) + 1.0
 
 
 @dataclass(frozen=True)
@@ -159,8 +189,113 @@ class LinearAttentionSpec:
 
 
 @dataclass(frozen=True)
+class LatentAttentionSpec:
+    """Causal softmax attention whose keys and values are made from one latent vector per position.
+
+    A query head has ``head_dim`` plain and ``rot_dim`` rotated elements.  The down projection ``kv_down_name`` gives
+    ``latent_size`` elements, RMS-normed with the weight ``kv_down_name`` + ``norm_suffix`` into the latent vector c, and
+    ``rot_dim`` more that are rotated and serve every head as the rotated part of its key.  Head h's plain key is
+    ``k_up_name``[h] c, its value ``v_up_name``[h] c (``v_head_dim`` elements); score = (q_plain . k_plain + q_rot . k_rot) *
+    ``softmax_scale``.  The cache holds c and the rotated part only.  ``output_gate``: the heads' outputs side by side are
+    multiplied by sigmoid(``gate_name`` h) before the output product."""
+    hidden_size: int
+    num_heads: int
+    head_dim: int
+    rot_dim: int
+    v_head_dim: int
+    latent_size: int
+    softmax_scale: float
+    norm_eps: float
+    position: Optional[PairRotarySpec] = None
+    output_gate: bool = True
+    q_name: str = "q"
+    kv_down_name: str = "dkv"
+    k_up_name: str = "uk"
+    v_up_name: str = "uv"
+    gate_name: str = "g"
+    o_name: str = "o"
+    norm_suffix: str = ".norm"
+    kind: str = "latent_attention"
+
+
+@dataclass(frozen=True)
+class SelectiveScanSpec:
+    """A state-space mixer with input-dependent step sizes: the in-projection gives [x | z] of ``inner`` channels each; x
+    passes a causal convolution of ``conv_taps`` taps per channel (with bias) and silu; ``x_name`` projects it to
+    [dt part (``dt_rank``) | B (``state_size``) | C (``state_size``)]; dt = softplus(``dt_name`` dt part + bias) per
+    channel; A = -exp(``a_log_name``) [inner, state_size]; S <- exp(dt A) S + dt x B, y = S C + D x; y silu(z) is projected
+    out.  The state S [inner, state_size] and the convolution's last taps - 1 inputs are kept per request, in float32."""
+    hidden_size: int
+    inner: int
+    state_size: int
+    dt_rank: int
+    conv_taps: int
+    in_name: str = "in"
+    conv_name: str = "conv"
+    x_name: str = "x"
+    dt_name: str = "dt"
+    a_log_name: str = "A_log"
+    d_name: str = "D"
+    o_name: str = "o"
+    bias_suffix: str = ".b"
+    kind: str = "selective_scan"
+
+
+@dataclass(frozen=True)
+class RoutedExpertsSpec:
+    """A feed-forward of ``num_experts`` small gated units of which each row uses ``top``: scores are sigmoid(router h) in
+    float32; the ``top`` largest choose the experts; an expert sees score * h (``scale_input``) and the outputs add up
+    without renormalising.  ``shared``: a gated unit that every row passes, added on top."""
+    hidden_size: int
+    num_experts: int
+    top: int
+    expert_size: int
+    act: str = "silu"
+    shared: Optional[object] = None
+    scale_input: bool = True
+    router_name: str = "router"
+    expert_prefix: str = "e{}."
+    shared_prefix: str = "shared."
+    gate_name: str = "gate"
+    up_name: str = "up"
+    down_name: str = "down"
+    kind: str = "routed_experts"
+
+
+@dataclass(frozen=True)
+class ReinjectSpec:
+    """A step between two layers that feeds the embedding's output in again: x <- W [x | x0] + b, with W ``weight_name``
+    [hidden, 2 hidden] and b row ``step_index`` of ``step_name`` [steps, hidden] (None: no b)."""
+    hidden_size: int
+    steps: int
+    step_index: int
+    weight_name: str = "loop.in"
+    step_name: Optional[str] = "loop.step"
+    kind: str = "reinject"
+
+
+@dataclass(frozen=True)
+class SandwichBlockSpec:
+    """One layer with a norm before and after each sublayer: x += norm_b(mixer(norm_a(x))); x += norm_d(ff(norm_c(x))).
+    ``feed_forward`` None: the layer has a mixer only."""
+    mixer: object
+    feed_forward: Optional[object]
+    mixer_norm: object
+    mixer_post_norm: object
+    ffn_norm: Optional[object]
+    ffn_post_norm: Optional[object]
+    mixer_prefix: str = "mix."
+    ffn_prefix: str = "mlp."
+    mixer_norm_prefix: str = "norm1"
+    mixer_post_norm_prefix: str = "norm1b"
+    ffn_norm_prefix: str = "norm2"
+    ffn_post_norm_prefix: str = "norm2b"
+    kind: str = "sandwich"
+
+
+@dataclass(frozen=True)
 class GLUSpec:
-    """down(act(gate(x)) * up(x)) with ``act`` "silu" or "gelu_tanh" (0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))))."""
+    """down(act(gate(x)) * up(x)) with ``act`` "silu", "relu" or "gelu_tanh" (0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))))."""
     hidden_size: int
     intermediate_size: int
     act: str = "gelu_tanh"
@@ -215,6 +350,7 @@ class RunEntry:
     layer: int
     cache: int
     writes_cache: bool = True
+    before: Optional[object] = None     # a step on the stream that runs before the layer (``ReinjectSpec``), or None
 
 
 @dataclass(frozen=True)
@@ -228,6 +364,7 @@ class ModelSpec:
     final_norm: object
     embed_scale: float = 1.0
     logit_scale: float = 1.0
+    logit_softcap: float = 0.0         # c > 0: logits <- c tanh(logits / c)
     tie_embeddings: bool = False
     embed_name: str = "model.embed_tokens.weight"
     lm_head_name: str = "lm_head.weight"

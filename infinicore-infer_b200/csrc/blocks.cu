@@ -1,0 +1,875 @@
+// Kernels of blocks whose sublayers sit between two RMS norms, of attention over one small latent vector per token,
+// of selective state-space scans and of routed experts:
+//
+//   norm_add            stream += rmsnorm(sublayer output) * w, and in the same pass the next sublayer's input
+//                       rmsnorm(stream) * w'
+//   concat_cast         [a | b] side by side as a product's operand; add_bias_rows
+//   latent_qkv          queries split into their plain and rotated parts, the latent vector normed, the shared rotated
+//                       key part turned, both written into the row's place of the paged cache
+//   head_linear         one small product per head (the key and value maps of the latent attention moved to the
+//                       query's and the output's side), optionally times a sigmoid gate
+//   latent_attention    softmax attention of all heads over one cached row per position, whose leading elements are
+//                       the values too; keys may be split among blocks (latent_merge joins them)
+//   causal_conv         a short convolution over time per channel with bias and activation, and its tails
+//   selective_scan      S <- exp(dt A) S + dt x B, y = S C + D x per channel, with dt = softplus(W low + b) formed here
+//   route_topk, route_sort, expert products, expert_combine      experts chosen per token by their scores
+//   softcap             cap * tanh(logits / cap)
+//
+// Everything that the design wants in float32 is float32 here: norms, angles, scores and softmax weights, routers, the
+// scan's state, decays, step sizes and gates.  Products take operands of the activation type T (float or bfloat16) and
+// accumulate in float32.  A step's rows are laid out request after request (req_start), continue at req_pos, and keep
+// their state in slot slot_ids[request]; a whole prompt, a portion and a single token are one case.
+#include "common.cuh"
+
+#include <algorithm>
+
+JK_DEFINE_ERROR_BUFFER(jk_blocks)
+
+__device__ __forceinline__ float sigmoid_f(float z) { return 1.f / (1.f + expf(-z)); }
+__device__ __forceinline__ float silu_f(float z) { return z / (1.f + expf(-z)); }
+__device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(expf(z)); }
+
+enum BlockAct : int { BACT_NONE = 0, BACT_SILU = 1, BACT_GELU_TANH = 2, BACT_SIGMOID = 3, BACT_RELU = 4 };
+__device__ __forceinline__ float block_act(int act, float z) {
+    switch (act) {
+        case BACT_SILU: return silu_f(z);
+        case BACT_GELU_TANH: return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+        case BACT_SIGMOID: return sigmoid_f(z);
+        case BACT_RELU: return fmaxf(z, 0.f);
+        default: return z;
+    }
+}
+
+#define BLOCKS_BY_DTYPE(dtype, name, LAUNCH)                                      \
+    do {                                                                          \
+        if ((dtype) == JK_F32) { LAUNCH(float); }                                 \
+        else if ((dtype) == JK_BF16) { LAUNCH(__nv_bfloat16); }                   \
+        else JK_FAIL(JK_UNSUPPORTED, name ": dtype %d", (int)(dtype));            \
+    } while (0)
+
+// ---------------------------------------------------------------------------------------------------------------
+// x[r] += delta[r] / sqrt(mean(delta[r]^2) + eps) * w;  then, if `out` is given,
+// out[r] = T(x[r] / sqrt(mean(x[r]^2) + eps2) * w_next)   (w_next null: out[r] = T(x[r])).
+// One block per row; the row stays in shared memory between the passes.
+// ---------------------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void norm_add_kernel(const float *__restrict__ delta, float *__restrict__ x, const float *__restrict__ w, float eps,
+                                const float *__restrict__ w_next, float eps2, T *__restrict__ out, int d) {
+    pdl_trigger();
+    pdl_wait();
+    extern __shared__ __align__(16) float row_buf[];
+    __shared__ float scratch[33];
+    const size_t base = (size_t)blockIdx.x * d;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < d; c += blockDim.x) {
+        const float v = delta[base + c];
+        row_buf[c] = v;
+        ss += v * v;
+    }
+    const float inv = 1.f / sqrtf(block_sum(ss, scratch) / (float)d + eps);
+    float ss2 = 0.f;
+    for (int c = threadIdx.x; c < d; c += blockDim.x) {
+        const float nx = x[base + c] + row_buf[c] * inv * w[c];
+        x[base + c] = nx;
+        row_buf[c] = nx;
+        ss2 += nx * nx;
+    }
+    if (out == nullptr) return;
+    if (w_next == nullptr) {
+        for (int c = threadIdx.x; c < d; c += blockDim.x) out[base + c] = from_f32<T>(row_buf[c]);
+        return;
+    }
+    const float inv2 = 1.f / sqrtf(block_sum(ss2, scratch) / (float)d + eps2);
+    for (int c = threadIdx.x; c < d; c += blockDim.x) out[base + c] = from_f32<T>(row_buf[c] * inv2 * w_next[c]);
+}
+
+JK_EXPORT int jk_norm_add(const float *delta, float *x, const float *w, float eps, const float *w_next, float eps2, void *out,
+                          int dtype, int rows, int d, cudaStream_t stream) {
+    if (rows == 0) return JK_OK;
+    JK_REQUIRE(delta && x && w && rows > 0 && d > 0, "norm_add: rows %d, width %d", rows, d);
+    const size_t smem = (size_t)d * sizeof(float);
+    JK_REQUIRE(smem <= 200 * 1024, "norm_add: width %d does not fit shared memory", d);
+    const int threads = d >= 4096 ? 512 : (d >= 1024 ? 256 : 128);
+#define LAUNCH(T)                                                                                                              \
+    if (smem > 48 * 1024) cudaFuncSetAttribute(norm_add_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
+    jk_launch(norm_add_kernel<T>, dim3(rows), dim3(threads), smem, stream, delta, x, w, eps, w_next, eps2, (T *)out, d)
+    BLOCKS_BY_DTYPE(dtype, "norm_add", LAUNCH);
+#undef LAUNCH
+    JK_CHECK_LAUNCH("norm_add");
+    return JK_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// out[t] = T([a[t] | b[t]]): two float32 streams side by side as the operand of one product.
+// ---------------------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void concat_cast_kernel(const float *__restrict__ a, const float *__restrict__ b, T *__restrict__ out, int d, size_t total) {
+    pdl_trigger();
+    pdl_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = i / (2 * d);
+        const int c = (int)(i % (2 * d));
+        out[i] = from_f32<T>(c < d ? a[t * d + c] : b[t * d + c - d]);
+    }
+}
+
+JK_EXPORT int jk_concat_cast(const float *a, const float *b, void *out, int dtype, int rows, int d, cudaStream_t stream) {
+    if (rows == 0) return JK_OK;
+    JK_REQUIRE(a && b && out && rows > 0 && d > 0, "concat_cast: rows %d, width %d", rows, d);
+    const size_t total = (size_t)rows * 2 * d;
+    const int blocks = (int)std::min<size_t>((total + 255) / 256, 148 * 16);
+#define LAUNCH(T) jk_launch(concat_cast_kernel<T>, dim3(blocks), dim3(256), 0, stream, a, b, (T *)out, d, total)
+    BLOCKS_BY_DTYPE(dtype, "concat_cast", LAUNCH);
+#undef LAUNCH
+    JK_CHECK_LAUNCH("concat_cast");
+    return JK_OK;
+}
+
+__global__ void add_bias_rows_kernel(float *__restrict__ x, const float *__restrict__ bias, int d, size_t total) {
+    pdl_trigger();
+    pdl_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) x[i] += bias[i % d];
+}
+
+JK_EXPORT int jk_add_bias_rows(float *x, const float *bias, int rows, int d, cudaStream_t stream) {
+    if (rows == 0) return JK_OK;
+    JK_REQUIRE(x && bias && rows > 0 && d > 0, "add_bias_rows: rows %d, width %d", rows, d);
+    const size_t total = (size_t)rows * d;
+    const int blocks = (int)std::min<size_t>((total + 255) / 256, 148 * 16);
+    jk_launch(add_bias_rows_kernel, dim3(blocks), dim3(256), 0, stream, x, bias, d, total);
+    JK_CHECK_LAUNCH("add_bias_rows");
+    return JK_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Queries and cache rows of the latent attention, from the float32 rows u [T, ld] of one fused product:
+//   u[t, q_off + h (dn + dr) + e]      head h of the query: dn plain elements, then dr that are rotated
+//   u[t, kv_off + e]                   e < R: the latent vector before its norm; then dr elements of the shared key part
+// Rotation of the first `rot_dims` of the dr elements in pairs (2i, 2i+1) by p * freq[i], formed in float32, with cos and
+// sin times `mag`.  Out: q_plain [T, H dn] (the operand of the per-head product that moves the key map to the query),
+// the rotated parts into q_full [T, H, R + dr] behind the R elements which that product fills, and the cache row of the
+// position, [latent * norm weight / rms | rotated key part], into pages [pages, page_size, R + dr].  One block per row.
+// ---------------------------------------------------------------------------------------------------------------
+struct LatentQkvArgs {
+    const float *u;
+    int ld, q_off, kv_off, H, dn, dr, R, rot_dims;
+    const float *freq;
+    float mag, eps;
+    const float *norm_w;
+    const int *positions, *row_req, *block_table;
+    int max_blocks, page_size;
+    void *q_plain, *q_full, *pages;
+};
+
+template <typename T>
+__global__ void latent_qkv_kernel(LatentQkvArgs a) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ float scratch[33];
+    const int t = blockIdx.x;
+    const float *u = a.u + (size_t)t * a.ld;
+    const int pos = a.positions[t];
+    const float fpos = (float)pos;
+    const int dq = a.dn + a.dr, D = a.R + a.dr;
+    // the latent vector's norm
+    float ss = 0.f;
+    for (int e = threadIdx.x; e < a.R; e += blockDim.x) {
+        const float v = u[a.kv_off + e];
+        ss += v * v;
+    }
+    const float inv = 1.f / sqrtf(block_sum(ss, scratch) / (float)a.R + a.eps);
+    const int page = a.block_table[(size_t)a.row_req[t] * a.max_blocks + pos / a.page_size];
+    T *crow = (T *)a.pages + ((size_t)page * a.page_size + (size_t)(pos % a.page_size)) * D;
+    for (int e = threadIdx.x; e < a.R; e += blockDim.x) crow[e] = from_f32<T>(u[a.kv_off + e] * inv * a.norm_w[e]);
+    // rotated parts: the shared key part (head index H) and every head's query part
+    for (int idx = threadIdx.x; idx < (a.H + 1) * a.dr; idx += blockDim.x) {
+        const int h = idx / a.dr, e = idx % a.dr;
+        const float *src = h == a.H ? u + a.kv_off + a.R : u + a.q_off + (size_t)h * dq + a.dn;
+        float val = src[e];
+        if (e < a.rot_dims) {
+            float sn, cs;
+            sincosf(fpos * a.freq[e >> 1], &sn, &cs);
+            sn *= a.mag; cs *= a.mag;
+            const float other = src[e ^ 1];
+            val = (e & 1) ? fmaf(val, cs, other * sn) : fmaf(val, cs, -other * sn);
+        }
+        if (h == a.H) crow[a.R + e] = from_f32<T>(val);
+        else ((T *)a.q_full)[((size_t)t * a.H + h) * D + a.R + e] = from_f32<T>(val);
+    }
+    for (int idx = threadIdx.x; idx < a.H * a.dn; idx += blockDim.x) {
+        const int h = idx / a.dn, e = idx % a.dn;
+        ((T *)a.q_plain)[(size_t)t * a.H * a.dn + idx] = from_f32<T>(u[a.q_off + (size_t)h * dq + e]);
+    }
+}
+
+JK_EXPORT int jk_latent_qkv(const float *u, int ld, int q_off, int kv_off, int H, int dn, int dr, int R, int rot_dims, const float *freq,
+                            float mag, const float *norm_w, float eps, const int *positions, const int *row_req, const int *block_table,
+                            int max_blocks, int page_size, void *q_plain, void *q_full, void *pages, int dtype, int T,
+                            cudaStream_t stream) {
+    if (T == 0) return JK_OK;
+    JK_REQUIRE(u && norm_w && positions && row_req && block_table && q_plain && q_full && pages, "latent_qkv: an argument is missing");
+    JK_REQUIRE(H > 0 && dn >= 0 && dr >= 0 && R > 0 && page_size > 0, "latent_qkv: heads %d, sizes %d + %d, latent %d", H, dn, dr, R);
+    JK_REQUIRE(rot_dims >= 0 && rot_dims <= dr && rot_dims % 2 == 0 && (rot_dims == 0 || freq), "latent_qkv: rotation of %d of %d elements", rot_dims, dr);
+    LatentQkvArgs a{u, ld, q_off, kv_off, H, dn, dr, R, rot_dims, freq, mag, eps, norm_w, positions, row_req, block_table,
+                    max_blocks, page_size, q_plain, q_full, pages};
+    const int work = H * (dn + dr);
+    const int threads = work >= 2048 ? 512 : (work >= 512 ? 256 : 128);
+#define LAUNCH(TT) jk_launch(latent_qkv_kernel<TT>, dim3(T), dim3(threads), 0, stream, a)
+    BLOCKS_BY_DTYPE(dtype, "latent_qkv", LAUNCH);
+#undef LAUNCH
+    JK_CHECK_LAUNCH("latent_qkv");
+    return JK_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Tiled products on the CUDA cores: C[M, N] = A[M, K] W[N, K]^T with float32 accumulation in the order of K, operands
+// of type T.  A block of 256 threads makes a tile of 64 x 64, a thread 4 x 4 of it; K passes shared memory 16 at a time.
+// Rows of A may be picked through an index (a_rows).  With GLU a second weight tile W2 runs along and the epilogue sees
+// both sums.  Used per head (head_linear) and per expert (expert products), where the problem depends on the block.
+// ---------------------------------------------------------------------------------------------------------------
+constexpr int GT_M = 64, GT_N = 64, GT_K = 16;
+
+template <typename T, bool GLU>
+__device__ __forceinline__ void tile_product(const T *__restrict__ A, size_t lda, const int *__restrict__ a_rows, int M,
+                                             const T *__restrict__ W, const T *__restrict__ W2, size_t ldw, int N, int K, int m0, int n0,
+                                             float (&acc)[4][4], float (&acc2)[4][4]) {
+    __shared__ float As[GT_K][GT_M + 4];
+    __shared__ float Ws[GT_K][GT_N + 4];
+    __shared__ float W2s[GLU ? GT_K : 1][GT_N + 4];
+    const int tid = threadIdx.x, ty = tid / 16, tx = tid % 16;
+    const int lr = tid / 4, lk = (tid % 4) * 4;      // this thread loads row lr, k lk .. lk + 3 of each operand tile
+    const int am = m0 + lr, wn = n0 + lr;
+    const T *arow = am < M ? A + (size_t)(a_rows ? a_rows[am] : am) * lda : nullptr;
+    const T *wrow = wn < N ? W + (size_t)wn * ldw : nullptr;
+    const T *w2row = (GLU && wn < N) ? W2 + (size_t)wn * ldw : nullptr;
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { acc[i][j] = 0.f; acc2[i][j] = 0.f; }
+    for (int k0 = 0; k0 < K; k0 += GT_K) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int k = k0 + lk + i;
+            As[lk + i][lr] = (arow && k < K) ? to_f32(arow[k]) : 0.f;
+            Ws[lk + i][lr] = (wrow && k < K) ? to_f32(wrow[k]) : 0.f;
+            if (GLU) W2s[lk + i][lr] = (w2row && k < K) ? to_f32(w2row[k]) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < GT_K; ++k) {
+            float av[4], wv[4], w2v[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { av[i] = As[k][ty * 4 + i]; wv[i] = Ws[k][tx * 4 + i]; if (GLU) w2v[i] = W2s[k][tx * 4 + i]; }
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    acc[i][j] = fmaf(av[i], wv[j], acc[i][j]);
+                    if (GLU) acc2[i][j] = fmaf(av[i], w2v[j], acc2[i][j]);
+                }
+        }
+        __syncthreads();
+    }
+}
+
+// out[t, h * out_hs + n] = T(sum_k in[t, h * K + k] * w[h, n, k]) (* sigmoid(gate[t * gate_ld + h * N + n]))
+template <typename T>
+__global__ void __launch_bounds__(256) head_linear_kernel(const T *__restrict__ in, const T *__restrict__ w, T *__restrict__ out, int rows, int H,
+                                                          int N, int K, int out_hs, const float *__restrict__ gate, int gate_ld) {
+    pdl_trigger();
+    pdl_wait();
+    const int h = blockIdx.z, m0 = blockIdx.x * GT_M, n0 = blockIdx.y * GT_N;
+    float acc[4][4], unused[4][4];
+    tile_product<T, false>(in + (size_t)h * K, (size_t)H * K, nullptr, rows, w + (size_t)h * N * K, nullptr, (size_t)K, N, K, m0, n0, acc, unused);
+    const int ty = threadIdx.x / 16, tx = threadIdx.x % 16;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int t = m0 + ty * 4 + i;
+        if (t >= rows) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int n = n0 + tx * 4 + j;
+            if (n >= N) continue;
+            float v = acc[i][j];
+            if (gate != nullptr) v *= sigmoid_f(gate[(size_t)t * gate_ld + (size_t)h * N + n]);
+            out[((size_t)t * H + h) * out_hs + n] = from_f32<T>(v);
+        }
+    }
+}
+
+JK_EXPORT int jk_head_linear(const void *in, const void *w, void *out, int dtype, int rows, int H, int N, int K, int out_hs,
+                             const float *gate, int gate_ld, cudaStream_t stream) {
+    if (rows == 0) return JK_OK;
+    JK_REQUIRE(in && w && out && rows > 0 && H > 0 && N > 0 && K > 0 && out_hs >= N, "head_linear: rows %d, heads %d, %d x %d into %d", rows, H, N, K, out_hs);
+    JK_REQUIRE(H <= 65535, "head_linear: %d heads exceed one launch", H);
+    dim3 grid((rows + GT_M - 1) / GT_M, (N + GT_N - 1) / GT_N, H);
+#define LAUNCH(T) jk_launch(head_linear_kernel<T>, grid, dim3(256), 0, stream, (const T *)in, (const T *)w, (T *)out, rows, H, N, K, out_hs, gate, gate_ld)
+    BLOCKS_BY_DTYPE(dtype, "head_linear", LAUNCH);
+#undef LAUNCH
+    JK_CHECK_LAUNCH("head_linear");
+    return JK_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Attention of H heads over one cached row per position: row j of a request is [c_j (R) | r_j (dr)]; a query row of a
+// head is [a (R) | b (dr)]; score = (a . c_j + b . r_j) * scale over j <= position; out = sum_j softmax_j c_j  [R].
+// A block takes one query row and LA_WARPS heads; 32 cached rows at a time pass shared memory (read once for all the
+// block's heads), a lane takes one of them for the scores and a slice of R for the weighted sum.  Scores, the running
+// maximum, the weights and the sums are float32.  With `splits` > 1 the keys of a row are cut into that many ranges
+// (blockIdx.z); a range leaves its unnormalised sum, maximum and normaliser in `part` and latent_merge joins them.
+// ---------------------------------------------------------------------------------------------------------------
+constexpr int LA_WARPS = 8;
+
+struct LatentAttnArgs {
+    const void *q, *pages;
+    void *out;
+    float *part;            // [T, H, splits, R + 2]
+    const int *positions, *row_req, *block_table;
+    int T, H, R, dr, page_size, max_blocks, splits;
+    float scale;
+};
+
+template <typename T, int NS>
+__global__ void __launch_bounds__(LA_WARPS * 32) latent_attention_kernel(LatentAttnArgs a) {
+    pdl_trigger();
+    pdl_wait();
+    extern __shared__ __align__(16) float la_smem[];
+    const int D = a.R + a.dr, DP = D + 1;
+    float *qs = la_smem;                                  // [LA_WARPS][D]
+    float *tile = la_smem + LA_WARPS * D;                 // [32][D + 1]
+    __shared__ long long row_off[32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int t = blockIdx.y, h = blockIdx.x * LA_WARPS + warp;
+    const bool active = h < a.H;
+    const int pos = a.positions[t];
+    const int *bt = a.block_table + (size_t)a.row_req[t] * a.max_blocks;
+    int lo = 0, hi = pos + 1;
+    if (a.splits > 1) {
+        const int chunk = (((pos + a.splits) / a.splits) + 31) / 32 * 32;
+        lo = blockIdx.z * chunk;
+        hi = min(pos + 1, lo + chunk);
+    }
+    if (active) {
+        const T *qrow = (const T *)a.q + ((size_t)t * a.H + h) * D;
+        for (int e = lane; e < D; e += 32) qs[warp * D + e] = to_f32(qrow[e]);
+    }
+    float m = -INFINITY, l = 0.f;
+    float acc[NS];
+#pragma unroll
+    for (int i = 0; i < NS; ++i) acc[i] = 0.f;
+    const T *pages = (const T *)a.pages;
+    for (int j0 = lo; j0 < hi; j0 += 32) {
+        const int n = min(32, hi - j0);
+        if (threadIdx.x < 32) {
+            const int j = j0 + threadIdx.x;
+            row_off[threadIdx.x] = threadIdx.x < n ? ((long long)bt[j / a.page_size] * a.page_size + (j % a.page_size)) * D : -1;
+        }
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < n * D; idx += blockDim.x) {
+            const int r = idx / D, e = idx % D;
+            tile[r * DP + e] = to_f32(pages[row_off[r] + e]);
+        }
+        __syncthreads();
+        if (active) {
+            float s = -INFINITY;
+            if (lane < n) {
+                const float *kr = tile + lane * DP, *qr = qs + warp * D;
+                float dot = 0.f;
+                for (int e = 0; e < D; ++e) dot = fmaf(qr[e], kr[e], dot);
+                s = dot * a.scale;
+            }
+            const float m_new = fmaxf(m, warp_max(s));
+            const float p = lane < n ? expf(s - m_new) : 0.f;
+            const float corr = expf(m - m_new);
+            l = l * corr + warp_sum(p);
+            m = m_new;
+#pragma unroll
+            for (int i = 0; i < NS; ++i) acc[i] *= corr;
+            for (int jj = 0; jj < n; ++jj) {
+                const float pj = __shfl_sync(0xffffffffu, p, jj);
+                const float *vr = tile + jj * DP;
+#pragma unroll
+                for (int i = 0; i < NS; ++i) {
+                    const int e = lane + 32 * i;
+                    if (e < a.R) acc[i] = fmaf(pj, vr[e], acc[i]);
+                }
+            }
+        }
+        __syncthreads();
+    }
+    if (!active) return;
+    if (a.splits > 1) {
+        float *p = a.part + (((size_t)t * a.H + h) * a.splits + blockIdx.z) * (a.R + 2);
+#pragma unroll
+        for (int i = 0; i < NS; ++i) {
+            const int e = lane + 32 * i;
+            if (e < a.R) p[e] = acc[i];
+        }
+        if (lane == 0) { p[a.R] = m; p[a.R + 1] = l; }
+        return;
+    }
+    T *orow = (T *)a.out + ((size_t)t * a.H + h) * a.R;
+    const float inv = 1.f / l;
+#pragma unroll
+    for (int i = 0; i < NS; ++i) {
+        const int e = lane + 32 * i;
+        if (e < a.R) orow[e] = from_f32<T>(acc[i] * inv);
+    }
+}
+
+// one warp per (row, head): the ranges' sums brought to one maximum and added in the order of the ranges
+template <typename T>
+__global__ void latent_merge_kernel(const float *__restrict__ part, T *__restrict__ out, int rows_heads, int R, int splits) {
+    pdl_trigger();
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int idx = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (idx >= rows_heads) return;
+    const float *p = part + (size_t)idx * splits * (R + 2);
+    float M = -INFINITY;
+    for (int s = 0; s < splits; ++s) M = fmaxf(M, p[(size_t)s * (R + 2) + R]);
+    float l = 0.f;
+    for (int s = 0; s < splits; ++s) {
+        const float ms = p[(size_t)s * (R + 2) + R];
+        if (ms > -INFINITY) l += p[(size_t)s * (R + 2) + R + 1] * expf(ms - M);
+    }
+    const float inv = 1.f / l;
+    for (int e = lane; e < R; e += 32) {
+        float v = 0.f;
+        for (int s = 0; s < splits; ++s) {
+            const float ms = p[(size_t)s * (R + 2) + R];
+            if (ms > -INFINITY) v = fmaf(p[(size_t)s * (R + 2) + e], expf(ms - M), v);
+        }
+        out[(size_t)idx * R + e] = from_f32<T>(v * inv);
+    }
+}
+
+// floats of `part` that `splits` ranges of T rows need
+JK_EXPORT long long jk_latent_attention_scratch(int T, int H, int R, int splits) {
+    return splits > 1 ? (long long)T * H * splits * (R + 2) : 0;
+}
+
+JK_EXPORT int jk_latent_attention(const void *q, const void *pages, void *out, float *part, int dtype, const int *positions,
+                                  const int *row_req, const int *block_table, int max_blocks, int page_size, int T, int H, int R,
+                                  int dr, float scale, int splits, cudaStream_t stream) {
+    if (T == 0) return JK_OK;
+    JK_REQUIRE(q && pages && out && positions && row_req && block_table, "latent_attention: an argument is missing");
+    JK_REQUIRE(H > 0 && R > 0 && dr >= 0 && page_size > 0 && max_blocks > 0, "latent_attention: heads %d, latent %d + %d", H, R, dr);
+    JK_REQUIRE(R <= 1024, "latent_attention: a latent size of %d exceeds 1024", R);
+    JK_REQUIRE(T <= 65535, "latent_attention: %d rows exceed one launch (65535)", T);
+    if (splits < 1) splits = 1;
+    JK_REQUIRE(splits == 1 || part != nullptr, "latent_attention: split keys need room for their parts");
+    JK_REQUIRE(splits <= 65535, "latent_attention: %d ranges", splits);
+    LatentAttnArgs a{q, pages, out, part, positions, row_req, block_table, T, H, R, dr, page_size, max_blocks, splits, scale};
+    const int D = R + dr;
+    const size_t smem = ((size_t)LA_WARPS * D + 32 * (size_t)(D + 1)) * sizeof(float);
+    JK_REQUIRE(smem <= 220 * 1024, "latent_attention: rows of %d elements do not fit shared memory", D);
+    dim3 grid((H + LA_WARPS - 1) / LA_WARPS, T, splits);
+#define LAUNCH_NS(TT, NS)                                                                                                                   \
+    do {                                                                                                                                    \
+        if (smem > 48 * 1024) cudaFuncSetAttribute(latent_attention_kernel<TT, NS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        jk_launch(latent_attention_kernel<TT, NS>, grid, dim3(LA_WARPS * 32), smem, stream, a);                                             \
+    } while (0)
+#define LAUNCH(TT)                                  \
+    if (R <= 64) LAUNCH_NS(TT, 2);                  \
+    else if (R <= 128) LAUNCH_NS(TT, 4);            \
+    else if (R <= 256) LAUNCH_NS(TT, 8);            \
+    else if (R <= 512) LAUNCH_NS(TT, 16);           \
+    else LAUNCH_NS(TT, 32)
+    BLOCKS_BY_DTYPE(dtype, "latent_attention", LAUNCH);
+#undef LAUNCH
+#undef LAUNCH_NS
+    JK_CHECK_LAUNCH("latent_attention");
+    if (splits > 1) {
+        const int n = T * H;
+#define LAUNCH(TT) jk_launch(latent_merge_kernel<TT>, dim3((n + 3) / 4), dim3(128), 0, stream, (const float *)part, (TT *)out, n, R, splits)
+        BLOCKS_BY_DTYPE(dtype, "latent_merge", LAUNCH);
+#undef LAUNCH
+        JK_CHECK_LAUNCH("latent_merge");
+    }
+    return JK_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// A short causal convolution over time on each of C channels, with bias and activation:
+//     y_t[c] = act(bias[c] + sum_j taps[c, j] * u_(t - J + 1 + j)[c])          zeros before the sequence starts
+// u is a column range of float32 rows [T, ld].  The J - 1 rows before a portion come from the request's tail
+// [slots, J - 1, C] (s = J - 2 the newest), which conv_tails then moves forward.  y goes out as float32 (what a
+// recurrence reads) and in the activation type (what a product reads).
+// ---------------------------------------------------------------------------------------------------------------
+struct ConvArgs {
+    const float *u;
+    int ld, off, C, J, act;
+    const float *taps, *bias;
+    float *tail;
+    const int *row_req, *req_start, *slot_ids;
+    float *y32;
+    void *yT;
+};
+
+template <typename T>
+__global__ void causal_conv_kernel(ConvArgs a, int rows) {
+    pdl_trigger();
+    pdl_wait();
+    const size_t total = (size_t)rows * a.C;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const int t = (int)(i / a.C), c = (int)(i % a.C);
+        const int req = a.row_req[t];
+        const int back = t - a.req_start[req];
+        const float *tail = a.J > 1 ? a.tail + (size_t)a.slot_ids[req] * (a.J - 1) * a.C : nullptr;
+        float acc = a.bias ? a.bias[c] : 0.f;
+        for (int j = 0; j < a.J; ++j) {
+            const int d = a.J - 1 - j;          // rows back
+            const float uv = d <= back ? a.u[(size_t)(t - d) * a.ld + a.off + c] : tail[(size_t)(a.J - 1 + back - d) * a.C + c];
+            acc = fmaf(a.taps[(size_t)c * a.J + j], uv, acc);
+        }
+        const float y = block_act(a.act, acc);
+        if (a.y32) a.y32[i] = y;
+        if (a.yT) ((T *)a.yT)[i] = from_f32<T>(y);
+    }
+}
+
+// tail[slot, s, c] <- the input J - 1 - s rows before the end of the request's sequence after this step; a thread owns
+// (request, channel) and reads every old entry before it overwrites it
+__global__ void conv_tails_kernel(ConvArgs a, int nreq) {
+    pdl_trigger();
+    pdl_wait();
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= nreq * a.C) return;
+    const int req = idx / a.C, c = idx % a.C;
+    const int first = a.req_start[req], n = a.req_start[req + 1] - first;
+    float *tail = a.tail + (size_t)a.slot_ids[req] * (a.J - 1) * a.C;
+    for (int s = 0; s < a.J - 1; ++s) {
+        const int off = n - (a.J - 1) + s;
+        const float v = off >= 0 ? a.u[(size_t)(first + off) * a.ld + a.off + c] : tail[(size_t)(s + n) * a.C + c];
+        tail[(size_t)s * a.C + c] = v;
+    }
+}
+
+JK_EXPORT int jk_causal_conv(const float *u, int ld, int off, int C, const float *taps, const float *bias, int J, int act, float *tail,
+                             const int *row_req, const int *req_start, const int *slot_ids, float *y32, void *yT, int dtype, int T,
+                             int nreq, cudaStream_t stream) {
+    if (T == 0) return JK_OK;
+    JK_REQUIRE(u && taps && row_req && req_start && C > 0 && J >= 1 && (y32 || yT), "causal_conv: an argument is missing");
+    JK_REQUIRE(J == 1 || (tail && slot_ids), "causal_conv: %d taps without the tails' state", J);
+    ConvArgs a{u, ld, off, C, J, act, taps, bias, tail, row_req, req_start, slot_ids, y32, yT};
+    const size_t total = (size_t)T * C;
+    const int blocks = (int)std::min<size_t>((total + 255) / 256, 148 * 16);
+#define LAUNCH(TT) jk_launch(causal_conv_kernel<TT>, dim3(blocks), dim3(256), 0, stream, a, T)
+    BLOCKS_BY_DTYPE(dtype, "causal_conv", LAUNCH);
+#undef LAUNCH
+    JK_CHECK_LAUNCH("causal_conv");
+    if (J > 1) {
+        jk_launch(conv_tails_kernel, dim3((nreq * C + 127) / 128), dim3(128), 0, stream, a, nreq);
+        JK_CHECK_LAUNCH("conv_tails");
+    }
+    return JK_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Selective scan.  Per request, channel c of E and state n of N, over the request's rows in order:
+//     dt_t[c]  = softplus(sum_k Wdt[c, k] low_t[k] + bdt[c])                low_t = [dt part (K) | B_t (N) | C_t (N)]
+//     S[c, n] <- exp(dt_t[c] A[c, n]) S[c, n] + dt_t[c] x_t[c] B_t[n]
+//     y_t[c]   = sum_n S[c, n] C_t[n] + Dskip[c] x_t[c];   out_t[c] = T(y_t[c] * silu(z_t[c]))
+// all float32; S lives in state[slot, c, n] between steps.  Eight neighbouring lanes share a channel: lane `part` keeps
+// the states part, part + 8, ... in registers and a share of the K products; sums go around by shuffles.  A block of 256
+// threads owns 32 channels of one request and walks the request's rows.
+// ---------------------------------------------------------------------------------------------------------------
+constexpr int SS_LANES = 8;
+
+struct ScanArgs {
+    const float *x;         // [T, E] after convolution and activation
+    const float *low;       // [T, ld_low]
+    int ld_low, K, N, E;
+    const float *z;         // z_t[c] = z[t * ld_z + c]
+    int ld_z;
+    const float *Wdt, *bdt, *A, *Dskip;
+    float *state;
+    const int *req_start, *slot_ids;
+    void *out;
+};
+
+template <typename T, int NPER>
+__global__ void __launch_bounds__(256) selective_scan_kernel(ScanArgs a) {
+    pdl_trigger();
+    pdl_wait();
+    const int req = blockIdx.y;
+    const int part = threadIdx.x % SS_LANES;
+    const int c = blockIdx.x * (256 / SS_LANES) + threadIdx.x / SS_LANES;
+    const bool live = c < a.E;
+    const int cc = live ? c : a.E - 1;          // idle lanes follow a real channel so that the shuffles stay whole
+    const int first = a.req_start[req], last = a.req_start[req + 1];
+    float *S = a.state + ((size_t)a.slot_ids[req] * a.E + cc) * a.N;
+    float s[NPER], An[NPER];
+#pragma unroll
+    for (int i = 0; i < NPER; ++i) {
+        const int n = part + SS_LANES * i;
+        s[i] = n < a.N ? S[n] : 0.f;
+        An[i] = n < a.N ? a.A[(size_t)cc * a.N + n] : 0.f;
+    }
+    const float bias = a.bdt[cc], dskip = a.Dskip[cc];
+    const float *wdt = a.Wdt + (size_t)cc * a.K;
+    for (int t = first; t < last; ++t) {
+        const float *low = a.low + (size_t)t * a.ld_low;
+        float d = 0.f;
+        for (int k = part; k < a.K; k += SS_LANES) d = fmaf(wdt[k], low[k], d);
+#pragma unroll
+        for (int o = SS_LANES / 2; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+        const float dt = softplus_f(d + bias);
+        const float xv = a.x[(size_t)t * a.E + cc];
+        const float dx = dt * xv;
+        const float *Bt = low + a.K, *Ct = low + a.K + a.N;
+        float y = 0.f;
+#pragma unroll
+        for (int i = 0; i < NPER; ++i) {
+            const int n = part + SS_LANES * i;
+            if (n < a.N) {
+                s[i] = fmaf(expf(dt * An[i]), s[i], dx * Bt[n]);
+                y = fmaf(s[i], Ct[n], y);
+            }
+        }
+#pragma unroll
+        for (int o = SS_LANES / 2; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
+        if (live && part == 0) {
+            y = fmaf(dskip, xv, y);
+            ((T *)a.out)[(size_t)t * a.E + c] = from_f32<T>(y * silu_f(a.z[(size_t)t * a.ld_z + c]));
+        }
+    }
+    if (live) {
+#pragma unroll
+        for (int i = 0; i < NPER; ++i) {
+            const int n = part + SS_LANES * i;
+            if (n < a.N) S[n] = s[i];
+        }
+    }
+}
+
+JK_EXPORT int jk_selective_scan(const float *x, const float *low, int ld_low, int K, int N, int E, const float *z, int ld_z,
+                                const float *Wdt, const float *bdt, const float *A, const float *Dskip, float *state,
+                                const int *req_start, const int *slot_ids, int nreq, void *out, int dtype, cudaStream_t stream) {
+    if (nreq == 0) return JK_OK;
+    JK_REQUIRE(x && low && z && Wdt && bdt && A && Dskip && state && req_start && slot_ids && out, "selective_scan: an argument is missing");
+    JK_REQUIRE(K > 0 && N > 0 && E > 0 && ld_low >= K + 2 * N, "selective_scan: rank %d, states %d, channels %d, rows of %d", K, N, E, ld_low);
+    JK_REQUIRE(N <= SS_LANES * 32, "selective_scan: %d states exceed %d", N, SS_LANES * 32);
+    JK_REQUIRE(nreq <= 65535, "selective_scan: %d requests exceed one launch", nreq);
+    ScanArgs a{x, low, ld_low, K, N, E, z, ld_z, Wdt, bdt, A, Dskip, state, req_start, slot_ids, out};
+    dim3 grid((E + 256 / SS_LANES - 1) / (256 / SS_LANES), nreq);
+    const int per = (N + SS_LANES - 1) / SS_LANES;
+#define LAUNCH_N(TT, NPER) jk_launch(selective_scan_kernel<TT, NPER>, grid, dim3(256), 0, stream, a)
+#define LAUNCH(TT)                              \
+    if (per <= 1) LAUNCH_N(TT, 1);              \
+    else if (per <= 2) LAUNCH_N(TT, 2);         \
+    else if (per <= 4) LAUNCH_N(TT, 4);         \
+    else if (per <= 8) LAUNCH_N(TT, 8);         \
+    else if (per <= 16) LAUNCH_N(TT, 16);       \
+    else LAUNCH_N(TT, 32)
+    BLOCKS_BY_DTYPE(dtype, "selective_scan", LAUNCH);
+#undef LAUNCH
+#undef LAUNCH_N
+    JK_CHECK_LAUNCH("selective_scan");
+    return JK_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Routed experts.  route_topk: one block per row; logits z_e = router[e] . h in float32, scores sigmoid(z_e); the `top`
+// experts of largest score (the lower index wins a tie) -> ids, scores [T, top], and the experts' counts.  route_sort:
+// one warp per expert lists its (row, choice) pairs in the order of the rows: entry -> source row, score; pair -> entry.
+// The experts' products then run over the entries, expert after expert, as tiles of the grouped kernels below; an
+// expert's input is score * h, which the first product applies to its sums (W (s h) = s (W h), in float32) before the
+// gate's activation.  expert_combine adds a row's `top` results in the order of its choices.
+// ---------------------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void route_topk_kernel(const T *__restrict__ h, const float *__restrict__ router, int D, int E, int top, int *__restrict__ ids,
+                                  float *__restrict__ scores, int *__restrict__ counts) {
+    pdl_trigger();
+    pdl_wait();
+    extern __shared__ float z[];        // [E]
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    const T *row = h + (size_t)t * D;
+    for (int e = warp; e < E; e += nwarp) {
+        const float *w = router + (size_t)e * D;
+        float dot = 0.f;
+        for (int c = lane; c < D; c += 32) dot = fmaf(w[c], to_f32(row[c]), dot);
+        dot = warp_sum(dot);
+        if (lane == 0) z[e] = dot;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int k = 0; k < top; ++k) {
+            int best = -1;
+            float bz = -INFINITY;
+            for (int e = 0; e < E; ++e)
+                if (best < 0 || z[e] > bz) { bz = z[e]; best = e; }
+            ids[(size_t)t * top + k] = best;
+            scores[(size_t)t * top + k] = sigmoid_f(bz);
+            atomicAdd(&counts[best], 1);
+            z[best] = -INFINITY;
+        }
+    }
+}
+
+// entry_row[pos], entry_score[pos] for pos in [starts[e], starts[e + 1]); pair_entry[pair] = pos
+__global__ void route_sort_kernel(const int *__restrict__ ids, const float *__restrict__ scores, const int *__restrict__ counts, int pairs,
+                                  int E, int top, int *__restrict__ starts, int *__restrict__ entry_row, float *__restrict__ entry_score,
+                                  int *__restrict__ pair_entry) {
+    pdl_trigger();
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int e = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (e >= E) return;
+    int start = 0;
+    for (int i = 0; i < e; ++i) start += counts[i];
+    if (lane == 0) {
+        starts[e] = start;
+        if (e == E - 1) starts[E] = start + counts[e];
+    }
+    int at = start;
+    for (int p0 = 0; p0 < pairs; p0 += 32) {
+        const int p = p0 + lane;
+        const bool mine = p < pairs && ids[p] == e;
+        const unsigned ballot = __ballot_sync(0xffffffffu, mine);
+        if (mine) {
+            const int pos = at + __popc(ballot & ((1u << lane) - 1u));
+            entry_row[pos] = p / top;
+            entry_score[pos] = scores[p];
+            pair_entry[p] = pos;
+        }
+        at += __popc(ballot);
+    }
+}
+
+// which expert's tile a block has: tiles of GT_M entries, expert after expert
+__device__ __forceinline__ bool expert_tile(const int *starts, int E, int block, int *expert, int *m0) {
+    int tiles = 0;
+    for (int e = 0; e < E; ++e) {
+        const int n = starts[e + 1] - starts[e];
+        const int mine = (n + GT_M - 1) / GT_M;
+        if (block < tiles + mine) { *expert = e; *m0 = (block - tiles) * GT_M; return true; }
+        tiles += mine;
+    }
+    return false;
+}
+
+// act[entry, n] = T(actf(s * g) * (s * u)), g = W_gate[e] h_row, u = W_up[e] h_row; w: [E, 2 ff, D] (gate rows, then up rows)
+template <typename T>
+__global__ void __launch_bounds__(256) expert_gate_up_kernel(const T *__restrict__ h, const T *__restrict__ w, T *__restrict__ act, int D, int ff, int E,
+                                                             const int *__restrict__ starts, const int *__restrict__ entry_row,
+                                                             const float *__restrict__ entry_score, int actf) {
+    pdl_trigger();
+    pdl_wait();
+    int e, m0;
+    if (!expert_tile(starts, E, blockIdx.x, &e, &m0)) return;
+    const int first = starts[e], M = starts[e + 1] - first, n0 = blockIdx.y * GT_N;
+    const T *we = w + (size_t)e * 2 * ff * D;
+    float g[4][4], u[4][4];
+    tile_product<T, true>(h, (size_t)D, entry_row + first, M, we, we + (size_t)ff * D, (size_t)D, ff, D, m0, n0, g, u);
+    const int ty = threadIdx.x / 16, tx = threadIdx.x % 16;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int r = m0 + ty * 4 + i;
+        if (r >= M) continue;
+        const float s = entry_score[first + r];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int n = n0 + tx * 4 + j;
+            if (n < ff) act[(size_t)(first + r) * ff + n] = from_f32<T>(block_act(actf, s * g[i][j]) * (s * u[i][j]));
+        }
+    }
+}
+
+// y[entry, n] = W_down[e] act[entry]; w: [E, D, ff]; float32 out
+template <typename T>
+__global__ void __launch_bounds__(256) expert_down_kernel(const T *__restrict__ act, const T *__restrict__ w, float *__restrict__ y, int D, int ff, int E,
+                                                          const int *__restrict__ starts) {
+    pdl_trigger();
+    pdl_wait();
+    int e, m0;
+    if (!expert_tile(starts, E, blockIdx.x, &e, &m0)) return;
+    const int first = starts[e], M = starts[e + 1] - first, n0 = blockIdx.y * GT_N;
+    float acc[4][4], unused[4][4];
+    tile_product<T, false>(act + (size_t)first * ff, (size_t)ff, nullptr, M, w + (size_t)e * D * ff, nullptr, (size_t)ff, D, ff, m0, n0, acc, unused);
+    const int ty = threadIdx.x / 16, tx = threadIdx.x % 16;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int r = m0 + ty * 4 + i;
+        if (r >= M) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int n = n0 + tx * 4 + j;
+            if (n < D) y[(size_t)(first + r) * D + n] = acc[i][j];
+        }
+    }
+}
+
+// delta[t] (+)= sum over the row's choices, in their order, of y[pair_entry[t * top + k]]
+__global__ void expert_combine_kernel(const float *__restrict__ y, const int *__restrict__ pair_entry, float *__restrict__ delta, int D, int top,
+                                      int add, size_t total) {
+    pdl_trigger();
+    pdl_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = i / D;
+        const int c = (int)(i % D);
+        float v = add ? delta[i] : 0.f;
+        for (int k = 0; k < top; ++k) v += y[(size_t)pair_entry[t * top + k] * D + c];
+        delta[i] = v;
+    }
+}
+
+// ints of workspace (`route`) that T rows need: counts [E], starts [E + 1], ids, entry_row, pair_entry [T top] and, as
+// floats, scores and entry_score [T top]
+JK_EXPORT long long jk_routed_experts_workspace(int T, int E, int top) { return 2LL * E + 1 + 5LL * T * top + 16; }
+
+// h [T, D] (type T) -> delta [T, D] float32 (add: on top of what is there).  entries [T top, D]-sized buffers: `act`
+// [T top, ff] of the activation type, `y` [T top, D] float32.
+JK_EXPORT int jk_routed_experts(const void *h, const float *router, const void *w_gate_up, const void *w_down, float *delta, int add,
+                                int dtype, int T, int D, int ff, int E, int top, int actf, int *route, void *act, float *y,
+                                cudaStream_t stream) {
+    if (T == 0) return JK_OK;
+    JK_REQUIRE(h && router && w_gate_up && w_down && delta && route && act && y, "routed_experts: an argument is missing");
+    JK_REQUIRE(D > 0 && ff > 0 && E > 0 && top > 0 && top <= E, "routed_experts: %d experts, %d a row, sizes %d and %d", E, top, D, ff);
+    JK_REQUIRE((size_t)E * sizeof(float) <= 40 * 1024, "routed_experts: %d experts exceed the router's shared memory", E);
+    const int pairs = T * top;
+    int *counts = route, *starts = counts + E, *ids = starts + E + 1, *entry_row = ids + pairs, *pair_entry = entry_row + pairs;
+    float *scores = (float *)(pair_entry + pairs), *entry_score = scores + pairs;
+    if (cudaMemsetAsync(counts, 0, sizeof(int) * (size_t)E, stream) != cudaSuccess) JK_FAIL(JK_CUDA_ERROR, "routed_experts: clearing the counts failed");
+#define LAUNCH(TT) jk_launch(route_topk_kernel<TT>, dim3(T), dim3(128), (size_t)E * sizeof(float), stream, (const TT *)h, router, D, E, top, ids, scores, counts)
+    BLOCKS_BY_DTYPE(dtype, "route_topk", LAUNCH);
+#undef LAUNCH
+    JK_CHECK_LAUNCH("route_topk");
+    jk_launch(route_sort_kernel, dim3((E + 3) / 4), dim3(128), 0, stream, (const int *)ids, (const float *)scores, (const int *)counts, pairs, E, top,
+              starts, entry_row, entry_score, pair_entry);
+    JK_CHECK_LAUNCH("route_sort");
+    const int tiles = (pairs + GT_M - 1) / GT_M + E;
+#define LAUNCH(TT)                                                                                                                          \
+    jk_launch(expert_gate_up_kernel<TT>, dim3(tiles, (ff + GT_N - 1) / GT_N), dim3(256), 0, stream, (const TT *)h, (const TT *)w_gate_up,  \
+              (TT *)act, D, ff, E, (const int *)starts, (const int *)entry_row, (const float *)entry_score, actf);                          \
+    jk_launch(expert_down_kernel<TT>, dim3(tiles, (D + GT_N - 1) / GT_N), dim3(256), 0, stream, (const TT *)act, (const TT *)w_down, y, D, \
+              ff, E, (const int *)starts)
+    BLOCKS_BY_DTYPE(dtype, "expert products", LAUNCH);
+#undef LAUNCH
+    JK_CHECK_LAUNCH("expert products");
+    const size_t total = (size_t)T * D;
+    jk_launch(expert_combine_kernel, dim3((int)std::min<size_t>((total + 255) / 256, 148 * 16)), dim3(256), 0, stream, (const float *)y,
+              (const int *)pair_entry, delta, D, top, add, total);
+    JK_CHECK_LAUNCH("expert_combine");
+    return JK_OK;
+}
+// kernels that one call of jk_routed_experts launches (the clearing of the counts included)
+JK_EXPORT int jk_routed_experts_launches() { return 6; }
+
+// ---------------------------------------------------------------------------------------------------------------
+// logits <- cap * tanh(logits / cap)
+// ---------------------------------------------------------------------------------------------------------------
+__global__ void softcap_kernel(float *__restrict__ x, float cap, size_t total) {
+    pdl_trigger();
+    pdl_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) x[i] = cap * tanhf(x[i] / cap);
+}
+
+JK_EXPORT int jk_softcap(float *x, float cap, long long n, cudaStream_t stream) {
+    if (n == 0) return JK_OK;
+    JK_REQUIRE(x && n > 0 && cap > 0.f, "softcap: %lld values, cap %f", n, (double)cap);
+    jk_launch(softcap_kernel, dim3((int)std::min<long long>((n + 255) / 256, 148 * 16)), dim3(256), 0, stream, x, cap, (size_t)n);
+    JK_CHECK_LAUNCH("softcap");
+    return JK_OK;
+}

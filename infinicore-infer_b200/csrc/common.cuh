@@ -125,16 +125,20 @@ template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(flo
 }
 
 // ---- the gate of a gated feed-forward -------------------------------------------------------
-// act(gate) * up with act = silu (GATE_SILU) or the tanh form of gelu (GATE_GELU_TANH).  The products whose epilogue is
-// a gated unit take the activation in the bits above the epilogue's own code: `epilogue | (gate_act << 8)`.
-enum JkGateAct : int { GATE_SILU = 0, GATE_GELU_TANH = 2 };
+// act(gate) * up with act = silu (GATE_SILU), the tanh form of gelu (GATE_GELU_TANH) or relu (GATE_RELU).  The products
+// whose epilogue is a gated unit take the activation in the bits above the epilogue's own code: `epilogue | (gate_act << 8)`.
+enum JkGateAct : int { GATE_SILU = 0, GATE_GELU_TANH = 2, GATE_RELU = 4 };
 __device__ __forceinline__ float gated_unit(int act, float gate, float up) {
     if (act == GATE_GELU_TANH)
         return 0.5f * gate * (1.f + tanhf(0.7978845608028654f * (gate + 0.044715f * gate * gate * gate))) * up;
+    if (act == GATE_RELU) return fmaxf(gate, 0.f) * up;
     return gate / (1.f + expf(-gate)) * up;
 }
 static inline int jk_epilogue_code(int epilogue) { return epilogue & 0xff; }
-static inline int jk_epilogue_gate(int epilogue) { return (epilogue >> 8) == GATE_GELU_TANH ? GATE_GELU_TANH : GATE_SILU; }
+static inline int jk_epilogue_gate(int epilogue) {
+    const int act = epilogue >> 8;
+    return act == GATE_GELU_TANH ? GATE_GELU_TANH : (act == GATE_RELU ? GATE_RELU : GATE_SILU);
+}
 
 // ---- reductions ------------------------------------------------------------------------
 __device__ __forceinline__ float warp_sum(float v) {

@@ -27,12 +27,13 @@ __device__ __forceinline__ float gelu_tanh_f(float z) {
 // log(sigmoid(z)) without overflow on either side
 __device__ __forceinline__ float log_sigmoid_f(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
 
-enum MixAct : int { ACT_NONE = 0, ACT_SILU = 1, ACT_GELU_TANH = 2, ACT_SIGMOID = 3 };
+enum MixAct : int { ACT_NONE = 0, ACT_SILU = 1, ACT_GELU_TANH = 2, ACT_SIGMOID = 3, ACT_RELU = 4 };
 __device__ __forceinline__ float apply_act(int act, float z) {
     switch (act) {
         case ACT_SILU: return silu_f(z);
         case ACT_GELU_TANH: return gelu_tanh_f(z);
         case ACT_SIGMOID: return sigmoid_f(z);
+        case ACT_RELU: return fmaxf(z, 0.f);
         default: return z;
     }
 }

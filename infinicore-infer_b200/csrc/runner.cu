@@ -55,6 +55,11 @@ JK_EXPORT int jk_runner_bind(const RunnerFns *fns) {
                (f.layernorm != nullptr) == (f.conv_qkv != nullptr) && (f.layernorm != nullptr) == (f.linear_scan != nullptr) &&
                (f.layernorm != nullptr) == (f.norm_gate != nullptr) && (f.layernorm != nullptr) == (f.err_mixers != nullptr),
                "runner_bind: a module's entries come together");
+    {
+        void *const *first = (void *const *)&f.norm_add, *const *last = (void *const *)&f.err_blocks;
+        for (void *const *e = first; e <= last; ++e)
+            JK_REQUIRE((*e != nullptr) == (*first != nullptr), "runner_bind: a module's entries come together");
+    }
     g_bound = true;
     return JK_OK;
 }
@@ -336,10 +341,10 @@ int run_gate_up(Run &r, const RunnerOp &op, const FusedNorm &fused) {
     if (int rc = r.slot(op.in_slot, (long long)r.elem() * T * d, &h, "gate/up's activations")) return rc;
     if (int rc = r.slot(op.out_slot, (long long)r.elem() * T * di, &act, "the feed-forward's inner activations")) return rc;
     // the gate's activation rides above the epilogue's code (common.cuh: gated_unit)
-    JK_REQUIRE(op.act == RUNNER_ACT_NONE || op.act == RUNNER_ACT_SILU || op.act == RUNNER_ACT_GELU_TANH,
+    JK_REQUIRE(op.act == RUNNER_ACT_NONE || op.act == RUNNER_ACT_SILU || op.act == RUNNER_ACT_GELU_TANH || op.act == RUNNER_ACT_RELU,
                "runner: a gated unit with activation %d is not built", op.act);
-    const bool gelu = op.act == RUNNER_ACT_GELU_TANH;
-    const int gate_bits = gelu ? (RUNNER_ACT_GELU_TANH << 8) : 0;
+    const bool gelu = op.act == RUNNER_ACT_GELU_TANH || op.act == RUNNER_ACT_RELU;      // not silu: the unfused unit is the mixers module's
+    const int gate_bits = gelu ? (op.act << 8) : 0;
     if (fused.norm != nullptr) {
         RUN(linear_small, g_fns.linear_small_norm(h, op.w, act, T, di, d, di, 1 | gate_bits, fused.sumsq, fused.norm->eps, nullptr, nullptr, nullptr,
                                                   1.f, r.env.status, ro.sms, r.stream));
@@ -466,6 +471,156 @@ int run_linear_attention(Run &r, const RunnerOp &op) {
     return JK_OK;
 }
 
+// ---- records of csrc/blocks.cu --------------------------------------------------------------------------------
+int need_blocks(const char *what) {
+    JK_REQUIRE(g_fns.norm_add != nullptr, "runner: %s needs the blocks module, which was not bound", what);
+    return JK_OK;
+}
+
+int run_norm_add(Run &r, const RunnerOp &op) {
+    if (int rc = need_blocks("a norm that adds a sublayer's output")) return rc;
+    const int T = r.st.ntok;
+    void *delta, *h = nullptr;
+    if (int rc = r.slot(op.in_slot, 4LL * T * op.n, &delta, "a sublayer's output")) return rc;
+    if (op.out_slot >= 0)
+        if (int rc = r.slot(op.out_slot, (long long)r.elem() * T * op.n, &h, "the next sublayer's input")) return rc;
+    JK_REQUIRE(!r.pending, "runner: a norm over a sublayer's output while another product waits to be added");
+    RUN(blocks, g_fns.norm_add((const float *)delta, r.x(), op.vec, op.eps, op.vec2, op.eps2, h, r.env.dtype, T, op.n, r.stream));
+    return JK_OK;
+}
+
+int run_reinject(Run &r, const RunnerOp &op) {
+    if (int rc = need_blocks("feeding the embedding in again")) return rc;
+    const int T = r.st.ntok;
+    void *x0, *both;
+    if (int rc = r.slot(op.in_slot, 4LL * T * op.n, &x0, "the embedding's output")) return rc;
+    if (int rc = r.slot(SLOT_ACT, (long long)r.elem() * T * op.k, &both, "the stream beside the embedding's output")) return rc;
+    JK_REQUIRE(op.k == 2 * op.n, "runner: feeding the embedding in again takes a matrix of %d x %d, found %d x %d", op.n, 2 * op.n, op.n, op.k);
+    if (int rc = flush_pending(r, T, op.n)) return rc;
+    RUN(blocks, g_fns.concat_cast(r.x(), (const float *)x0, both, r.env.dtype, T, op.n, r.stream));
+    if (r.env.dtype == JK_F32) {
+        RUN(elementwise, g_fns.gemm_f32((const float *)both, op.k, (const float *)op.w, op.k, op.vec, r.x(), op.n, T, op.n, op.k, r.stream));
+        return JK_OK;
+    }
+    if (int rc = product_f32(r, both, op.w, nullptr, r.x(), T, op.n, op.k)) return rc;
+    if (op.vec != nullptr) RUN(blocks, g_fns.add_bias_rows(r.x(), op.vec, T, op.n, r.stream));
+    return JK_OK;
+}
+
+int run_latent_qkv(Run &r, const RunnerOp &op) {
+    if (int rc = need_blocks("a latent attention's queries")) return rc;
+    const int T = r.st.ntok, H = op.heads, D = op.rank + op.rot_width;
+    void *u, *q_full, *q_plain;
+    if (int rc = r.slot(op.in_slot, 4LL * T * op.ld, &u, "the query and latent projection")) return rc;
+    if (int rc = r.slot(op.out_slot, (long long)r.elem() * T * H * D, &q_full, "the queries")) return rc;
+    if (int rc = r.slot(op.out2_slot, (long long)r.elem() * T * H * op.head_dim, &q_plain, "the queries' plain parts")) return rc;
+    const int *table = r.st.block_tables[op.cache_group];
+    JK_REQUIRE(table != nullptr, "runner: a latent attention writes the cache of group %d, whose block table the step lacks", op.cache_group);
+    RUN(blocks, g_fns.latent_qkv((const float *)u, op.ld, op.q_off, op.k_off, H, op.head_dim, op.rot_width, op.rank, op.rot_dims, op.freq,
+                                 op.rot_mag, op.norm_k, op.eps, r.st.positions, r.st.row_req, table, r.env.max_blocks, r.env.page_size,
+                                 q_plain, q_full, op.k_pages, r.env.dtype, T, r.stream));
+    return JK_OK;
+}
+
+int run_head_linear(Run &r, const RunnerOp &op) {
+    if (int rc = need_blocks("a product per head")) return rc;
+    const int T = r.st.ntok;
+    void *in, *out;
+    if (int rc = r.slot(op.in_slot, (long long)r.elem() * T * op.heads * op.k, &in, "a per-head product's operand")) return rc;
+    if (int rc = r.slot(op.out_slot, (long long)r.elem() * T * op.heads * op.out_hs, &out, "a per-head product's output")) return rc;
+    const float *gate = nullptr;
+    if (op.gated) {
+        void *u;
+        if (int rc = r.slot(SLOT_TMP, 4LL * T * op.ld, &u, "the projection that holds the gate")) return rc;
+        gate = (const float *)u + op.g_off;
+    }
+    RUN(blocks, g_fns.head_linear(in, op.w, out, r.env.dtype, T, op.heads, op.n, op.k, op.out_hs, gate, op.ld, r.stream));
+    return JK_OK;
+}
+
+// How many ranges the keys of a row are cut into: steps of few rows fill the SMs with ranges of at least 256 keys.
+int latent_splits(int T, int heads, int context, int sms) {
+    if (T > 16) return 1;
+    const int blocks = T * ((heads + 7) / 8);
+    const int want = (2 * sms + blocks - 1) / blocks, by_length = (context + 255) / 256;
+    return std::max(1, std::min(std::min(want, by_length), 64));
+}
+
+int run_latent_attention(Run &r, const RunnerOp &op) {
+    if (int rc = need_blocks("a latent attention")) return rc;
+    const int T = r.st.ntok, H = op.heads, D = op.rank + op.rot_width;
+    void *q, *o;
+    if (int rc = r.slot(op.in_slot, (long long)r.elem() * T * H * D, &q, "the queries")) return rc;
+    if (int rc = r.slot(op.out_slot, (long long)r.elem() * T * H * op.rank, &o, "a latent attention's output")) return rc;
+    const int *table = r.st.block_tables[op.cache_group];
+    JK_REQUIRE(table != nullptr, "runner: a latent attention reads the cache of group %d, whose block table the step lacks", op.cache_group);
+    const int splits = latent_splits(T, H, r.st.context > 0 ? r.st.context : op.max_positions, r.env.routing.sms);
+    void *part = nullptr;
+    if (splits > 1)
+        if (int rc = r.slot(SLOT_DECODE, 4 * g_fns.latent_attention_scratch(T, H, op.rank, splits), &part, "the ranges of a latent attention")) return rc;
+    RUN(blocks, g_fns.latent_attention(q, op.k_pages, o, (float *)part, r.env.dtype, r.st.positions, r.st.row_req, table, r.env.max_blocks,
+                                       r.env.page_size, T, H, op.rank, op.rot_width, op.softmax_scale, splits, r.stream));
+    if (splits > 1) ++g_launches;
+    return JK_OK;
+}
+
+int run_causal_conv(Run &r, const RunnerOp &op) {
+    if (int rc = need_blocks("a convolution over time")) return rc;
+    const int T = r.st.ntok;
+    void *u, *y32 = nullptr, *yT = nullptr;
+    if (int rc = r.slot(op.in_slot, 4LL * T * op.ld, &u, "a convolution's input")) return rc;
+    if (op.out2_slot >= 0)
+        if (int rc = r.slot(op.out2_slot, 4LL * T * op.n, &y32, "a convolution's float32 output")) return rc;
+    if (op.out_slot >= 0)
+        if (int rc = r.slot(op.out_slot, (long long)r.elem() * T * op.n, &yT, "a convolution's output")) return rc;
+    JK_REQUIRE(r.st.slot_ids != nullptr || op.taps <= 1, "runner: a convolution keeps tails, but the step names no state slots");
+    RUN(blocks, g_fns.causal_conv((const float *)u, op.ld, op.q_off, op.n, op.conv_q, op.bias, op.taps, op.act, op.state, r.st.row_req,
+                                  r.st.req_start, r.st.slot_ids, (float *)y32, yT, r.env.dtype, T, r.st.nreq, r.stream));
+    if (op.taps > 1) ++g_launches;
+    return JK_OK;
+}
+
+int run_selective_scan(Run &r, const RunnerOp &op) {
+    if (int rc = need_blocks("a selective scan")) return rc;
+    const int T = r.st.ntok, ld_low = op.rank + 2 * op.k;
+    void *x, *low, *u, *out;
+    if (int rc = r.slot(op.in_slot, 4LL * T * op.n, &x, "a scan's input")) return rc;
+    if (int rc = r.slot(op.in2_slot, 4LL * T * ld_low, &low, "a scan's step sizes and maps")) return rc;
+    if (int rc = r.slot(SLOT_TMP, 4LL * T * op.ld, &u, "the projection that holds a scan's gate")) return rc;
+    if (int rc = r.slot(op.out_slot, (long long)r.elem() * T * op.n, &out, "a scan's output")) return rc;
+    JK_REQUIRE(r.st.slot_ids != nullptr && op.state != nullptr, "runner: a scan without its state slots");
+    RUN(blocks, g_fns.selective_scan((const float *)x, (const float *)low, ld_low, op.rank, op.k, op.n, (const float *)u + op.g_off, op.ld,
+                                     (const float *)op.w2, op.b2, op.decay, op.vec, op.state, r.st.req_start, r.st.slot_ids, r.st.nreq, out,
+                                     r.env.dtype, r.stream));
+    return JK_OK;
+}
+
+int run_experts(Run &r, const RunnerOp &op) {
+    if (int rc = need_blocks("routed experts")) return rc;
+    const int T = r.st.ntok;
+    void *h, *delta, *route, *act, *y;
+    if (int rc = r.slot(op.in_slot, (long long)r.elem() * T * op.n, &h, "the experts' input")) return rc;
+    if (int rc = r.slot(SLOT_DELTA, 4LL * T * op.n, &delta, "the experts' output")) return rc;
+    if (int rc = r.slot(SLOT_ROUTE, 4 * g_fns.routed_experts_workspace(T, op.experts, op.top), &route, "the rows' choice of experts")) return rc;
+    if (int rc = r.slot(SLOT_ACT, (long long)r.elem() * T * op.top * op.ff, &act, "the experts' inner activations")) return rc;
+    if (int rc = r.slot(SLOT_TMP, 4LL * T * op.top * op.n, &y, "the experts' results")) return rc;
+    JK_REQUIRE(!r.pending, "runner: routed experts while another product waits to be added");
+    RUN(blocks, g_fns.routed_experts(h, op.vec, op.w, op.w3, (float *)delta, op.add, r.env.dtype, T, op.n, op.ff, op.experts, op.top, op.act,
+                                     (int *)route, act, (float *)y, r.stream));
+    g_launches += g_fns.routed_experts_launches() - 1;
+    return JK_OK;
+}
+
+int run_softcap(Run &r, const RunnerOp &op) {
+    if (int rc = need_blocks("a cap on the logits")) return rc;
+    const int rows = op.wanted_rows ? r.st.n_want : r.st.ntok;
+    if (rows == 0) return JK_OK;
+    void *x;
+    if (int rc = r.slot(op.in_slot, 4LL * rows * op.n, &x, "the logits")) return rc;
+    RUN(blocks, g_fns.softcap((float *)x, op.cap, (long long)rows * op.n, r.stream));
+    return JK_OK;
+}
+
 }  // namespace
 
 JK_EXPORT int jk_runner_run(const RunnerEnv *envp, const RunnerOp *ops, int first, int count, const RunnerStep *sp,
@@ -541,6 +696,21 @@ JK_EXPORT int jk_runner_run(const RunnerEnv *envp, const RunnerOp *ops, int firs
             case OP_LINEAR_ATTENTION:
                 rc = run_linear_attention(r, op);
                 break;
+            case OP_NORM_ADD:
+                hidden = op.n;
+                rc = run_norm_add(r, op);
+                break;
+            case OP_REINJECT:
+                hidden = op.n;
+                rc = run_reinject(r, op);
+                break;
+            case OP_LATENT_QKV: rc = run_latent_qkv(r, op); break;
+            case OP_HEAD_LINEAR: rc = run_head_linear(r, op); break;
+            case OP_LATENT_ATTENTION: rc = run_latent_attention(r, op); break;
+            case OP_CAUSAL_CONV: rc = run_causal_conv(r, op); break;
+            case OP_SELECTIVE_SCAN: rc = run_selective_scan(r, op); break;
+            case OP_EXPERTS: rc = run_experts(r, op); break;
+            case OP_SOFTCAP: rc = run_softcap(r, op); break;
             default:
                 JK_FAIL(JK_BAD_ARGUMENT, "runner_run: record %d has kind %d", i, op.kind);
         }
@@ -604,6 +774,41 @@ JK_EXPORT int jk_runner_slot_bytes(const RunnerEnv *env, const RunnerOp *ops, in
                     need(SLOT_SCAN, 4 * jk::scan_scratch_floats(rows, op.heads, op.head_dim, op.v_head_dim > 0 ? op.v_head_dim : op.head_dim, op.rank > 0));
                 break;
             }
+            case OP_NORM_ADD:
+                need(SLOT_X, 4LL * max_rows * op.n); need(op.in_slot, 4 * rows * op.n);
+                if (op.out_slot >= 0) need(op.out_slot, e * rows * op.n);
+                break;
+            case OP_REINJECT: need(SLOT_X, 4 * rows * op.n); need(op.in_slot, 4 * rows * op.n); need(SLOT_ACT, e * rows * op.k); break;
+            case OP_LATENT_QKV:
+                need(op.in_slot, 4 * rows * op.ld); need(op.out_slot, e * rows * op.heads * (op.rank + op.rot_width));
+                need(op.out2_slot, e * rows * op.heads * op.head_dim);
+                break;
+            case OP_HEAD_LINEAR:
+                need(op.in_slot, e * rows * op.heads * op.k); need(op.out_slot, e * rows * op.heads * op.out_hs);
+                break;
+            case OP_LATENT_ATTENTION: {
+                need(op.in_slot, e * rows * op.heads * (op.rank + op.rot_width)); need(op.out_slot, e * rows * op.heads * op.rank);
+                long long worst = 0;
+                for (int n = 1; n <= 16 && n <= max_rows; ++n)
+                    worst = std::max(worst, (long long)n * op.heads * latent_splits(n, op.heads, op.max_positions, env->routing.sms) * (op.rank + 2));
+                need(SLOT_DECODE, 4 * worst);
+                break;
+            }
+            case OP_CAUSAL_CONV:
+                need(op.in_slot, 4 * rows * op.ld);
+                if (op.out_slot >= 0) need(op.out_slot, e * rows * op.n);
+                if (op.out2_slot >= 0) need(op.out2_slot, 4 * rows * op.n);
+                break;
+            case OP_SELECTIVE_SCAN:
+                need(op.in_slot, 4 * rows * op.n); need(op.in2_slot, 4 * rows * (op.rank + 2 * op.k)); need(SLOT_TMP, 4 * rows * op.ld);
+                need(op.out_slot, e * rows * op.n);
+                break;
+            case OP_EXPERTS:
+                need(op.in_slot, e * rows * op.n); need(SLOT_DELTA, 4 * rows * op.n);
+                need(SLOT_ROUTE, 4 * (2LL * op.experts + 1 + 5 * rows * op.top + 16));
+                need(SLOT_ACT, e * rows * op.top * op.ff); need(SLOT_TMP, 4 * rows * op.top * op.n);
+                break;
+            case OP_SOFTCAP: need(op.in_slot, 4 * rows * op.n); break;
             default: JK_FAIL(JK_BAD_ARGUMENT, "runner_slot_bytes: record %d has kind %d", i, op.kind);
         }
     }
@@ -617,7 +822,7 @@ JK_EXPORT int jk_runner_needs_gemm_tcgen05(const RunnerEnv *env, const RunnerOp 
         const RunnerOp &op = ops[i];
         int kind;
         switch (op.kind) {
-            case OP_QKV: case OP_LINEAR: kind = jk::PRODUCT_F32; break;
+            case OP_QKV: case OP_LINEAR: case OP_REINJECT: kind = jk::PRODUCT_F32; break;
             case OP_RESIDUAL: kind = jk::PRODUCT_RESIDUAL; break;
             case OP_GATE_UP: kind = jk::PRODUCT_SWIGLU; break;
             default: continue;

@@ -57,6 +57,25 @@ typedef int (*LinearScanFn)(const float *, int, int, int, int, int, int, int, in
                             int, int, float, float *, const int *, const int *, int, int, float *, const int *, int, const int *, int,
                             const int *, int, float *, long long, int, cudaStream_t);
 typedef int (*NormGateFn)(const float *, const float *, int, int, const float *, float, int, int, int, int, void *, int, int, cudaStream_t);
+// csrc/blocks.cu
+typedef int (*NormAddFn)(const float *, float *, const float *, float, const float *, float, void *, int, int, int, cudaStream_t);
+typedef int (*ConcatCastFn)(const float *, const float *, void *, int, int, int, cudaStream_t);
+typedef int (*AddBiasRowsFn)(float *, const float *, int, int, cudaStream_t);
+typedef int (*LatentQkvFn)(const float *, int, int, int, int, int, int, int, int, const float *, float, const float *, float, const int *,
+                           const int *, const int *, int, int, void *, void *, void *, int, int, cudaStream_t);
+typedef int (*HeadLinearFn)(const void *, const void *, void *, int, int, int, int, int, int, const float *, int, cudaStream_t);
+typedef int (*LatentAttentionFn)(const void *, const void *, void *, float *, int, const int *, const int *, const int *, int, int, int,
+                                 int, int, int, float, int, cudaStream_t);
+typedef long long (*LatentScratchFn)(int, int, int, int);
+typedef int (*CausalConvFn)(const float *, int, int, int, const float *, const float *, int, int, float *, const int *, const int *,
+                            const int *, float *, void *, int, int, int, cudaStream_t);
+typedef int (*SelectiveScanFn)(const float *, const float *, int, int, int, int, const float *, int, const float *, const float *,
+                               const float *, const float *, float *, const int *, const int *, int, void *, int, cudaStream_t);
+typedef int (*RoutedExpertsFn)(const void *, const float *, const void *, const void *, float *, int, int, int, int, int, int, int, int,
+                               int *, void *, float *, cudaStream_t);
+typedef long long (*RoutedWorkspaceFn)(int, int, int);
+typedef int (*CountFn)();
+typedef int (*SoftcapFn)(float *, float, long long, cudaStream_t);
 typedef int (*ArgmaxFn)(const float *, long long, int, int, int *, void *, cudaStream_t);
 typedef int (*SampleFn)(const float *, long long, int, int, const float *, const int *, const float *, const float *, int *,
                         cudaStream_t);
@@ -100,6 +119,22 @@ struct RunnerFns {
     LinearScanFn linear_scan;
     NormGateFn norm_gate;
     LastErrorFn err_mixers;
+    // norms around sublayers, latent attention, selective scans, routed experts (csrc/blocks.cu): bound together, and
+    // only for a model whose records name them
+    NormAddFn norm_add;
+    ConcatCastFn concat_cast;
+    AddBiasRowsFn add_bias_rows;
+    LatentQkvFn latent_qkv;
+    HeadLinearFn head_linear;
+    LatentAttentionFn latent_attention;
+    LatentScratchFn latent_attention_scratch;
+    CausalConvFn causal_conv;
+    SelectiveScanFn selective_scan;
+    RoutedExpertsFn routed_experts;
+    RoutedWorkspaceFn routed_experts_workspace;
+    CountFn routed_experts_launches;
+    SoftcapFn softcap;
+    LastErrorFn err_blocks;
 };
 
 // ---- records ---------------------------------------------------------------------------------------------------
@@ -118,7 +153,9 @@ enum RunnerSlot {
     SLOT_TMP,           // float32: the product before an unfused rotation or activation ([T, widest such product])
     SLOT_DECODE,        // float32: partial results of the split-key attention
     SLOT_MIX,           // float32 [T, heads * value size]: a recurrence's output before its norm and gate
-    SLOT_SCAN,          // float32: the states and running decays of a recurrence's pieces
+    SLOT_SCAN,          // float32: the states and running decays of a recurrence's pieces; a scan's small projections
+    SLOT_X0,            // float32 [T, hidden]: the embedding's output, for a model that feeds it in again later
+    SLOT_ROUTE,         // int32 and float32: which experts each row chose, and the rows of each expert
     RUNNER_SLOTS
 };
 
@@ -137,9 +174,24 @@ enum RunnerOpKind {
                         // partial rotation; q -> out, k and v -> their pages; the convolution's tails move forward
     OP_LINEAR_ATTENTION,// in: float32 rows [q | k | v | gate | ...]; S = diag(a) S + k v^T, o = S^T q per head over each
                         // request's rows and its state slot; out = rmsnorm(o) * w * act(gate)
+    OP_NORM_ADD,        // in = SLOT_DELTA: stream += rmsnorm(in) * vec; if out_slot >= 0: out = rmsnorm(stream) * vec2 (the next
+                        // sublayer's input; vec2 null: out = activations(stream))
+    OP_REINJECT,        // stream = [stream | in] w^T + vec, in = SLOT_X0: the embedding's output fed in again
+    OP_LATENT_QKV,      // in: float32 rows [q | latent and shared key part | ...]; the heads' plain query parts -> out2, their
+                        // rotated parts -> out (behind the `rank` elements OP_HEAD_LINEAR fills); the normed latent vector and
+                        // the rotated key part -> the row's place in the pages
+    OP_HEAD_LINEAR,     // out[t, h, 0..n) = in[t, h, 0..k) w[h]^T for every head (w [heads, n, k]), rows of out `out_hs` apart
+                        // per head; gated: times sigmoid(SLOT_TMP[t, g_off + h n + j])
+    OP_LATENT_ATTENTION,// out[t, h] = softmax(q[t, h] . page rows * scale, causal) (page rows' first `rank` elements)
+    OP_CAUSAL_CONV,     // in: float32 rows; n channels at q_off pass `taps` taps over time (+ bias, act); out = activations,
+                        // out2 = float32; the request's tails (state) move forward
+    OP_SELECTIVE_SCAN,  // in = x [T, n] float32, in2 = [dt part (rank) | B (k) | C (k)] float32, z = SLOT_TMP[t, g_off + c];
+                        // S = exp(dt A) S + dt x B, y = S C + D x over each request's rows and its state slot; out = y silu(z)
+    OP_EXPERTS,         // SLOT_DELTA (+)= sum over each row's `top` experts of largest sigmoid(vec in) of expert(score * in)
+    OP_SOFTCAP,         // logits = cap * tanh(logits / cap) over the wanted rows
 };
 
-enum RunnerAct { RUNNER_ACT_NONE = 0, RUNNER_ACT_SILU = 1, RUNNER_ACT_GELU_TANH = 2, RUNNER_ACT_SIGMOID = 3 };
+enum RunnerAct { RUNNER_ACT_NONE = 0, RUNNER_ACT_SILU = 1, RUNNER_ACT_GELU_TANH = 2, RUNNER_ACT_SIGMOID = 3, RUNNER_ACT_RELU = 4 };
 
 struct RunnerOp {
     int kind;
@@ -181,6 +233,22 @@ struct RunnerOp {
     const float *b2;            // LINEAR_ATTENTION: [heads * head_dim]
     const float *bias;          // LAYERNORM: the bias
     float *state;               // CONV_QKV: tails [slots, taps - 1, channels]; LINEAR_ATTENTION: [slots, heads, dk, dv]
+    // ---- what the records of csrc/blocks.cu add; read by those records only ------------------------------------------
+    int in2_slot, out2_slot;    // a second input / output (LATENT_QKV, CAUSAL_CONV, SELECTIVE_SCAN)
+    int rot_width;              // LATENT_QKV, LATENT_ATTENTION: elements of a head (and of a cached row) behind the plain ones
+    int experts, top, ff;       // EXPERTS: how many there are, how many a row takes, their inner width
+    int add;                    // EXPERTS: 1 adds to what SLOT_DELTA holds (a shared expert's output), 0 overwrites
+    int out_hs;                 // HEAD_LINEAR: elements between two heads of an output row
+    float eps2;                 // NORM_ADD: eps of the second norm
+    float rot_mag;              // LATENT_QKV: factor of cos and sin
+    float cap;                  // SOFTCAP
+    const float *vec2;          // NORM_ADD: the next sublayer's norm weight
+    const void *w3;             // EXPERTS: the experts' down matrices [experts, hidden, ff] (w: [experts, 2 ff, hidden])
+    // NORM_ADD: vec = the norm's weight.  REINJECT: vec = the row added to every row.  LATENT_QKV: heads, head_dim (plain
+    // part), rank (latent size), rot_dims, freq, norm_k (the latent norm's weight), eps, q_off, k_off (the latent's column).
+    // CAUSAL_CONV: conv_q = taps [n, taps], bias, act, state = tails [slots, taps - 1, n].  SELECTIVE_SCAN: n channels, k
+    // states, w2 = the step size's projection [n, rank] (float32), b2 its bias, decay = A [n, k], vec = D, state [slots, n, k].
+    // EXPERTS: n = hidden, vec = the router [experts, hidden] (float32), act = the experts' activation.
 };
 
 // What does not change from step to step and is no part's business.

@@ -30,6 +30,7 @@ MODULES: Dict[str, List[str]] = {
     "gemm_tcgen05": ["gemm_tcgen05.cu", "gemm_skinny.cu"],
     "attention_tcgen05": ["attention_tcgen05.cu"],
     "mixers": ["mixers.cu"],
+    "blocks": ["blocks.cu"],
     "runner": ["runner.cu", "capi.cu", "reference_abi.cu"],
     "host": ["host.cpp"],
 }

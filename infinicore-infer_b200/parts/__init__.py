@@ -12,9 +12,15 @@ from .glu import GLU
 from .linear_attention import LinearAttention
 from .conv_attention import ConvAttention
 from .postnorm_block import PostNormBlock
+from .latent_attention import LatentAttention
+from .selective_scan import SelectiveScan
+from .routed_experts import RoutedExperts
+from .sandwich_block import SandwichBlock
+from .reinject import Reinject
 from .model import Model, cache_needs, model_manifest, state_needs
 
 __all__ = ["BLOCKS", "FEED_FORWARDS", "MIXERS", "NORMS", "POSITIONS", "ResidualStream", "Runtime", "StepContext", "Program",
            "ProgramRunner", "HostIO", "part_class", "register", "RMSNorm", "RotaryTables", "Attention", "SwiGLU",
-           "PreNormBlock", "LayerNorm", "GLU", "LinearAttention", "ConvAttention", "PostNormBlock", "Model", "cache_needs", "model_manifest",
+           "PreNormBlock", "LayerNorm", "GLU", "LinearAttention", "ConvAttention", "PostNormBlock", "LatentAttention",
+           "SelectiveScan", "RoutedExperts", "SandwichBlock", "Reinject", "Model", "cache_needs", "model_manifest",
            "state_needs"]

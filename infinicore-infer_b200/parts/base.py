@@ -10,6 +10,7 @@ it is in, not the other layers.  Four registries hold the four families:
                     forward(h, ctx, view, writes_cache) -> tensor [T, hidden]
     feed_forward    forward(h, ctx) -> tensor [T, hidden]
     block           forward(residual, ctx, view, writes_cache) -> None
+    stream          plan(program): a step on the stream between two layers (a run-order entry's ``before``)
 
 A part may also have ``plan(program, ...)`` (see ``parts/program.py``): it then says what it does as launch records
 that the native step replays, and its ``forward`` is the same records run alone.  A part without ``plan`` runs by its
@@ -32,9 +33,10 @@ POSITIONS: Dict[str, type] = {}
 MIXERS: Dict[str, type] = {}
 FEED_FORWARDS: Dict[str, type] = {}
 BLOCKS: Dict[str, type] = {}
+STREAM_STEPS: Dict[str, type] = {}      # steps on the stream between two layers: plan(program)
 
 _FAMILIES = {"norm": NORMS, "position": POSITIONS, "mixer": MIXERS,
-             "feed_forward": FEED_FORWARDS, "block": BLOCKS}
+             "feed_forward": FEED_FORWARDS, "block": BLOCKS, "stream": STREAM_STEPS}
 
 
 def register(family: str, kind: str) -> Callable[[type], type]:

@@ -1,4 +1,4 @@
-"""Gated feed-forward with a choice of activation: down(act(gate(h)) * up(h)), act silu or the tanh form of gelu.
+"""Gated feed-forward with a choice of activation: down(act(gate(h)) * up(h)), act silu, relu or the tanh form of gelu.
 
 One fused gate | up product, the gated unit, the down product into the slot of products that wait for the stream (the
 block decides how it is added: plainly, or through a norm).
@@ -23,7 +23,7 @@ class GLU:
 
     def __init__(self, spec, weights, prefix: str, runtime):
         self.spec, self.runtime = spec, runtime
-        if spec.act not in ("silu", "gelu_tanh"):
+        if spec.act not in ("silu", "gelu_tanh", "relu"):
             raise ValueError(f"a gated feed-forward with activation {spec.act!r} is not built")
         self.w_gate_up = weights.get_rows([prefix + spec.gate_name, prefix + spec.up_name], MATRIX)
         self.w_down = weights.get(prefix + spec.down_name, MATRIX)

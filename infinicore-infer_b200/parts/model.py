@@ -27,6 +27,9 @@ def model_manifest(spec) -> Dict[str, TensorDecl]:
         prefix = spec.layer_prefix.format(i)
         for name, decl in part_class("block", layer).tensor_decls(layer).items():
             out[prefix + name] = decl
+    for e in spec.order:          # steps between layers name their tensors without a layer's prefix
+        if e.before is not None:
+            out.update(part_class("stream", e.before).tensor_decls(e.before))
     return out
 
 
@@ -74,6 +77,9 @@ class Model:
                                                               spec.final_norm_prefix, runtime)
         self.layers = [part_class("block", layer)(layer, weights, spec.layer_prefix.format(i), runtime)
                        for i, layer in enumerate(spec.layers)]
+        shared: dict = {}          # tensors that several steps between layers use are loaded once
+        self.before = [None if e.before is None else part_class("stream", e.before)(e.before, weights, "", runtime, shared=shared)
+                       for e in spec.order]
 
     @property
     def graph_safe(self) -> bool:
@@ -84,6 +90,7 @@ class Model:
         total = self.lm_head.numel() * self.lm_head.element_size()
         for e in self.spec.order:
             total += getattr(self.layers[e.layer], "weight_bytes", lambda: 0)()
+        total += sum(b.weight_bytes() for b in self.before if b is not None and hasattr(b, "weight_bytes"))
         return total
 
     def plan(self, views, page_size: int, max_blocks: int, state_views=None) -> Program:
@@ -96,8 +103,14 @@ class Model:
         program.emit("jk_emit_embedding", ctypes.c_void_p(self.embedding.data_ptr()), ctypes.c_int(kernels.dtype_code(self.embedding.dtype)),
                      ctypes.c_int(spec.hidden_size), ctypes.c_float(spec.embed_scale), keep=(self.embedding,))
         hidden = spec.hidden_size
+        if any(getattr(b, "needs_embedding_output", False) for b in self.before):
+            from .program import record
+            program.emit_records([record("embed", None, "x0", n=hidden, w=self.embedding, w_dtype=kernels.dtype_code(self.embedding.dtype),
+                                         scale=spec.embed_scale)], keep=(self.embedding,))
         for index, e in enumerate(spec.order):
             layer, view = self.layers[e.layer], views[e.cache]
+            if self.before[index] is not None:
+                self.before[index].plan(program)
             own = state_views[index] if state_views else None
             if hasattr(layer, "plan"):
                 if own is not None or hasattr(type(layer), "state_need"):
@@ -112,6 +125,9 @@ class Model:
             program.host(_host_final_norm(self.final_norm, spec.logit_scale, hidden))
         program.emit("jk_emit_output", ctypes.c_void_p(self.lm_head.data_ptr()), ctypes.c_int(spec.vocab_size),
                      ctypes.c_int(spec.hidden_size), keep=(self.lm_head,))
+        if spec.logit_softcap:
+            from .program import record
+            program.emit_records([record("softcap", "logits", None, n=spec.vocab_size, cap=float(spec.logit_softcap), wanted_rows=True)])
         return program
 
 

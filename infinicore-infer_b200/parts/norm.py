@@ -17,11 +17,11 @@ from .base import ResidualStream, register
 class RMSNorm:
     @staticmethod
     def tensor_decls(spec) -> Dict[str, TensorDecl]:
-        return {"weight": TensorDecl((spec.size,), VECTOR, init="ones")}
+        return {spec.weight_name: TensorDecl((spec.size,), VECTOR, init="ones")}
 
     def __init__(self, spec, weights, prefix: str, runtime):
         self.spec, self.runtime = spec, runtime
-        self.weight = weights.get(prefix + "weight", VECTOR)
+        self.weight = weights.get(prefix + spec.weight_name, VECTOR)
 
     def weight_bytes(self) -> int:
         return self.weight.numel() * self.weight.element_size()
@@ -33,6 +33,20 @@ class RMSNorm:
         program.emit("jk_emit_rmsnorm", ctypes.c_void_p(self.weight.data_ptr()), ctypes.c_int(self.spec.size),
                      ctypes.c_float(self.spec.eps), ctypes.c_float(out_scale), ctypes.c_int(1 if wanted_rows else 0),
                      keep=(self.weight,))
+
+    def plan_add(self, program) -> None:
+        """One record: stream += rmsnorm(the product that waits in the delta slot) * weight.  The norm of the sublayer that
+        follows may join the record (``plan_after_add``)."""
+        from .program import record
+        program.emit_records([record("norm_add", "delta", None, n=self.spec.size, eps=self.spec.eps, vec=self.weight)], keep=(self.weight,))
+
+    def plan_after_add(self, program) -> None:
+        """This norm over every row, right after a ``plan_add``: it joins that record (the kernel holds the new stream's row
+        in shared memory), else it is a record of its own."""
+        if not program.amend_last("norm_add", out_slot="h", vec2=self.weight, eps2=self.spec.eps):
+            self.plan(program)
+        else:
+            program.keep.append(self.weight)
 
     def forward(self, residual: ResidualStream, ctx, out_scale: float = 1.0,
                 rows: Optional[torch.Tensor] = None) -> torch.Tensor:

@@ -24,13 +24,16 @@ from ..kernels import host as _host
 
 _i, _f, _p, _ll = ctypes.c_int, ctypes.c_float, ctypes.c_void_p, ctypes.c_longlong
 
-SLOTS = ("x", "delta", "h", "q", "o", "act", "hw", "logits", "tmp", "decode", "mix", "scan")       # RunnerSlot of csrc/runner.h
+SLOTS = ("x", "delta", "h", "q", "o", "act", "hw", "logits", "tmp", "decode", "mix", "scan", "x0", "route")       # RunnerSlot of csrc/runner.h
 SLOT = {name: i for i, name in enumerate(SLOTS)}
 OP_NAMES = {1: "embed", 2: "norm", 3: "qkv", 4: "attention", 5: "residual", 6: "gate_up", 7: "linear", 8: "cast",
-            9: "layernorm", 10: "conv_qkv", 11: "linear_attention"}
+            9: "layernorm", 10: "conv_qkv", 11: "linear_attention", 12: "norm_add", 13: "reinject", 14: "latent_qkv",
+            15: "head_linear", 16: "latent_attention", 17: "causal_conv", 18: "selective_scan", 19: "experts", 20: "softcap"}
 OP = {name: kind for kind, name in OP_NAMES.items()}                                # RunnerOpKind
-ACT = {"none": 0, "silu": 1, "gelu_tanh": 2, "sigmoid": 3}                          # RunnerAct
+ACT = {"none": 0, "silu": 1, "gelu_tanh": 2, "sigmoid": 3, "relu": 4}               # RunnerAct
 _MIXERS_OPS = (OP["cast"], OP["layernorm"], OP["conv_qkv"], OP["linear_attention"])
+_BLOCKS_OPS = tuple(OP[n] for n in ("norm_add", "reinject", "latent_qkv", "head_linear", "latent_attention", "causal_conv",
+                                    "selective_scan", "experts", "softcap"))
 MAX_GROUPS = 8
 MAX_LISTS = 8
 
@@ -46,7 +49,11 @@ class RunnerOp(ctypes.Structure):
                 + [(n, _i) for n in ("v_head_dim", "sink", "gated", "act", "gate_act", "ld", "q_off", "k_off", "v_off", "g_off", "r_off",
                                      "taps", "rot_dims", "per_head_norm", "rank", "has_kv", "list_aux")]
                 + [(n, _f) for n in ("tau", "q_scale")]
-                + [(n, _p) for n in ("conv_q", "conv_k", "conv_v", "norm_q", "norm_k", "freq", "decay", "w2", "b2", "bias", "state")])
+                + [(n, _p) for n in ("conv_q", "conv_k", "conv_v", "norm_q", "norm_k", "freq", "decay", "w2", "b2", "bias", "state")]
+                # what the records of csrc/blocks.cu add
+                + [(n, _i) for n in ("in2_slot", "out2_slot", "rot_width", "experts", "top", "ff", "add", "out_hs")]
+                + [(n, _f) for n in ("eps2", "rot_mag", "cap")]
+                + [(n, _p) for n in ("vec2", "w3")])
 
 
 class Routing(ctypes.Structure):
@@ -77,27 +84,29 @@ class _Fns(ctypes.Structure):
         "attention_tcgen05", "err_elementwise", "err_linear_small", "err_gemm_tcgen05", "err_attention", "err_attention_tcgen05",
         "linear_small_supports", "linear_small_qkv_supports", "gemm_skinny", "linear_small_norm_supports", "linear_small_norm",
         "linear_small_qkv_norm", "argmax", "sample", "err_sampling", "layernorm", "cast_rows", "glu", "conv_qkv", "linear_scan",
-        "norm_gate", "err_mixers")]
+        "norm_gate", "err_mixers", "norm_add", "concat_cast", "add_bias_rows", "latent_qkv", "head_linear", "latent_attention",
+        "latent_attention_scratch", "causal_conv", "selective_scan", "routed_experts", "routed_experts_workspace",
+        "routed_experts_launches", "softcap", "err_blocks")]
 
 
 def _addr(lib, name: str) -> int:
     return ctypes.cast(getattr(lib, name), ctypes.c_void_p).value
 
 
-_bound: Dict[str, bool] = {"base": False, "gemm_tcgen05": False, "attention_tcgen05": False, "mixers": False}
+_bound: Dict[str, bool] = {"base": False, "gemm_tcgen05": False, "attention_tcgen05": False, "mixers": False, "blocks": False}
 
 
-def runner_lib(gemm_tcgen05: bool = False, attention_tcgen05: bool = False, mixers: bool = False) -> ctypes.CDLL:
+def runner_lib(gemm_tcgen05: bool = False, attention_tcgen05: bool = False, mixers: bool = False, blocks: bool = False) -> ctypes.CDLL:
     """The native step's library with the kernel modules' entry points handed over.  The tcgen05 modules and the module of
     the mixers beyond softmax attention are bound (and so compiled) only when asked for: a model whose steps never reach
     them never builds them."""
     lib = _build.load("runner")
-    want = {"base": True, "gemm_tcgen05": gemm_tcgen05, "attention_tcgen05": attention_tcgen05, "mixers": mixers}
+    want = {"base": True, "gemm_tcgen05": gemm_tcgen05, "attention_tcgen05": attention_tcgen05, "mixers": mixers, "blocks": blocks}
     if all(_bound[k] or not want[k] for k in want):
         return lib
     lib.jk_runner_last_error.restype = ctypes.c_char_p
     names = ["elementwise", "linear_small", "attention", "sampling"] + (["gemm_tcgen05"] if gemm_tcgen05 else []) \
-        + (["attention_tcgen05"] if attention_tcgen05 else []) + (["mixers"] if mixers else [])
+        + (["attention_tcgen05"] if attention_tcgen05 else []) + (["mixers"] if mixers else []) + (["blocks"] if blocks else [])
     mods = {m: _build.load(m) for m in names}
     get = lambda module, name: _addr(mods[module], name) if module in mods else None
     fns = _Fns(
@@ -126,7 +135,14 @@ def runner_lib(gemm_tcgen05: bool = False, attention_tcgen05: bool = False, mixe
         err_sampling=get("sampling", "jk_sampling_last_error"),
         layernorm=get("mixers", "jk_layernorm"), cast_rows=get("mixers", "jk_cast_rows"), glu=get("mixers", "jk_glu"),
         conv_qkv=get("mixers", "jk_conv_qkv"), linear_scan=get("mixers", "jk_linear_scan"), norm_gate=get("mixers", "jk_norm_gate"),
-        err_mixers=get("mixers", "jk_mixers_last_error"))
+        err_mixers=get("mixers", "jk_mixers_last_error"),
+        norm_add=get("blocks", "jk_norm_add"), concat_cast=get("blocks", "jk_concat_cast"), add_bias_rows=get("blocks", "jk_add_bias_rows"),
+        latent_qkv=get("blocks", "jk_latent_qkv"), head_linear=get("blocks", "jk_head_linear"),
+        latent_attention=get("blocks", "jk_latent_attention"), latent_attention_scratch=get("blocks", "jk_latent_attention_scratch"),
+        causal_conv=get("blocks", "jk_causal_conv"), selective_scan=get("blocks", "jk_selective_scan"),
+        routed_experts=get("blocks", "jk_routed_experts"), routed_experts_workspace=get("blocks", "jk_routed_experts_workspace"),
+        routed_experts_launches=get("blocks", "jk_routed_experts_launches"), softcap=get("blocks", "jk_softcap"),
+        err_blocks=get("blocks", "jk_blocks_last_error"))
     if lib.jk_runner_bind(ctypes.byref(fns)):
         from ..kernels import KernelError
         raise KernelError(lib.jk_runner_last_error().decode(errors="replace"))
@@ -152,7 +168,10 @@ def record(kind: str, in_slot: str = None, out_slot: str = None, **fields) -> Ru
     op.in_slot = SLOT[in_slot] if in_slot is not None else -1
     op.out_slot = SLOT[out_slot] if out_slot is not None else -1
     op.scale = 1.0
+    op.in2_slot = op.out2_slot = -1
     for name, value in fields.items():
+        if name in ("in2_slot", "out2_slot"):
+            value = SLOT[value] if value is not None else -1
         if isinstance(value, torch.Tensor):
             value = value.data_ptr()
         elif isinstance(value, bool):
@@ -173,7 +192,7 @@ class HostIO:
         """``[rows, width]`` of a slot (the activations' type unless said otherwise; ``x`` and ``delta`` are float32)."""
         rows = self.rows if rows is None else rows
         if dtype is None:
-            dtype = torch.float32 if slot in ("x", "delta", "logits", "tmp", "decode", "mix", "scan") else self._runner.runtime.dtype
+            dtype = torch.float32 if slot in ("x", "delta", "logits", "tmp", "decode", "mix", "scan", "x0") else self._runner.runtime.dtype
         raw = self._runner.slot_tensor(slot)
         need = rows * width * torch.empty((), dtype=dtype).element_size()
         if need > raw.numel():
@@ -235,6 +254,24 @@ class Program:
         self._emitted(n)
         self.keep.extend(keep)
 
+    def amend_last(self, kind: str, **fields) -> bool:
+        """Set fields of the record emitted last if it is of ``kind`` and every named field is still unset (zero, or no slot):
+        how a part hands its work to the record before it (a norm whose input the preceding kernel holds in shared memory
+        anyway).  Returns whether it did."""
+        if not self.count or not self.items or self.items[-1][0] != "ops":
+            return False
+        last = self.ops[self.count - 1]
+        if last.kind != OP[kind]:
+            return False
+        fresh = record(kind, **fields)
+        for name in fields:
+            unset = -1 if name.endswith("_slot") else 0
+            if getattr(last, name) not in (unset, None):
+                return False
+        for name in fields:
+            setattr(last, name, getattr(fresh, name))
+        return True
+
     def host(self, fn: Callable) -> None:
         """A step of the model that its own Python code runs: ``fn(ctx, io)`` with ``io`` a ``HostIO``.  The stream is
         whole when it is called (no product waits for its addition) and must be whole when it returns."""
@@ -290,7 +327,8 @@ class ProgramRunner:
             for i in range(program.count))
         need_mixers = any(program.ops[i].kind in _MIXERS_OPS or (program.ops[i].kind == OP["gate_up"] and program.ops[i].act > ACT["silu"])
                           for i in range(program.count))
-        self.lib = runner_lib(need_gemm, need_attn, need_mixers)
+        need_blocks = any(program.ops[i].kind in _BLOCKS_OPS for i in range(program.count))
+        self.lib = runner_lib(need_gemm, need_attn, need_mixers, need_blocks)
         self.lib.jk_runner_last_error.restype = ctypes.c_char_p
         sizes = (_ll * len(SLOTS))()
         self._check(self.lib.jk_runner_slot_bytes(ctypes.byref(self.env), program.ops, program.count, max_rows, self.max_want, sizes))

@@ -1,0 +1,69 @@
+"""A feed-forward of small gated units (experts) of which each row uses a few, chosen by a router.
+
+Scores are sigmoid(router h) in float32; a row goes to the ``top`` experts of largest score; an expert sees score * h;
+the results add up without renormalising.  A shared gated unit, if the layer has one, runs for every row first (the
+feed-forward's usual two records) and the experts' sum is added to it.  The rows of each expert are listed on the
+device, so a step never waits for the host; the experts' products run over those lists (csrc/blocks.cu).
+"""
+from __future__ import annotations
+
+from typing import Dict
+
+import torch
+
+from ..weights import MATRIX, VECTOR, TensorDecl
+from .base import part_class, register
+from .program import ACT, record
+
+
+@register("feed_forward", "routed_experts")
+class RoutedExperts:
+    @staticmethod
+    def tensor_decls(spec) -> Dict[str, TensorDecl]:
+        d, f = spec.hidden_size, spec.expert_size
+        decls = {spec.router_name: TensorDecl((spec.num_experts, d), VECTOR)}
+        for e in range(spec.num_experts):
+            p = spec.expert_prefix.format(e)
+            decls[p + spec.gate_name] = TensorDecl((f, d))
+            decls[p + spec.up_name] = TensorDecl((f, d))
+            decls[p + spec.down_name] = TensorDecl((d, f))
+        if spec.shared is not None:
+            for name, decl in part_class("feed_forward", spec.shared).tensor_decls(spec.shared).items():
+                decls[spec.shared_prefix + name] = decl
+        return decls
+
+    def __init__(self, spec, weights, prefix: str, runtime):
+        self.spec, self.runtime = spec, runtime
+        if not spec.scale_input:
+            raise ValueError("routed experts whose score multiplies the output are not built")
+        if not 1 <= spec.top <= spec.num_experts:
+            raise ValueError(f"{spec.top} of {spec.num_experts} experts")
+        self.router = weights.get(prefix + spec.router_name, VECTOR)
+        names = [prefix + spec.expert_prefix.format(e) for e in range(spec.num_experts)]
+        self.w_gate_up = weights.get_rows([p + n for p in names for n in (spec.gate_name, spec.up_name)], MATRIX)
+        self.w_down = weights.get_rows([p + spec.down_name for p in names], MATRIX)
+        self.shared = None
+        if spec.shared is not None:
+            self.shared = part_class("feed_forward", spec.shared)(spec.shared, weights, prefix + spec.shared_prefix, runtime)
+            if not hasattr(self.shared, "plan_delta"):
+                raise TypeError(f"{type(self.shared).__name__} cannot leave its output for the experts to add to (no plan_delta)")
+
+    def weight_bytes(self) -> int:
+        """What a step of few rows reads: the router, the shared unit, ``top`` experts a row at most (here: one row's)."""
+        s = self.spec
+        one = (self.w_gate_up.numel() + self.w_down.numel()) * self.w_gate_up.element_size() // s.num_experts
+        return 4 * self.router.numel() + s.top * one + (self.shared.weight_bytes() if self.shared is not None else 0)
+
+    def plan_delta(self, program) -> None:
+        s = self.spec
+        if self.shared is not None:
+            self.shared.plan_delta(program)
+        program.emit_records([
+            record("experts", "h", "delta", n=s.hidden_size, experts=s.num_experts, top=s.top, ff=s.expert_size, vec=self.router,
+                   w=self.w_gate_up, w3=self.w_down, add=self.shared is not None, act=ACT[s.act]),
+        ], keep=(self.router, self.w_gate_up, self.w_down))
+
+    def forward(self, h: torch.Tensor, ctx) -> torch.Tensor:
+        """The part alone: its own records over ``h``; float32 ``[T, hidden]``."""
+        from .program import run_part_alone
+        return run_part_alone(self.runtime, self.plan_delta, ctx, h, self.spec.hidden_size, result_slot="delta")
