@@ -646,6 +646,110 @@ def norm_gate(o: torch.Tensor, u: torch.Tensor, g_off: int, weight: torch.Tensor
     return out
 
 
+# ---- csrc/blocks.cu ---------------------------------------------------------------------------------------------------
+ACT_RELU = 4
+
+
+def norm_add(delta: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, eps: float, next_weight: Optional[torch.Tensor] = None,
+             next_eps: float = 0.0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x += rmsnorm(delta) * weight; with ``out``: out = rmsnorm(x) * next_weight (or x itself) in out's type."""
+    _need(delta, "delta", torch.float32); _need(x, "x", torch.float32); _need(weight, "weight", torch.float32)
+    rows, d = x.shape
+    lib = _build.load("blocks")
+    _check("blocks", lib.jk_norm_add(_ptr(delta), _ptr(x), _ptr(weight), _c_float(eps), _ptr(next_weight), _c_float(next_eps), _ptr(out),
+                                     _c_int(dtype_code(out.dtype) if out is not None else F32), _c_int(rows), _c_int(d), _stream()))
+    return x
+
+
+def latent_qkv(u: torch.Tensor, q_off: int, kv_off: int, heads: int, dn: int, dr: int, latent: int, rot_dims: int,
+               freq: Optional[torch.Tensor], magnitude: float, norm_weight: torch.Tensor, eps: float, positions, row_req, block_table,
+               page_size: int, q_plain: torch.Tensor, q_full: torch.Tensor, pages: torch.Tensor) -> None:
+    """Queries and cache rows of a latent attention from the fused float32 projection ``u`` (see csrc/blocks.cu)."""
+    _need(u, "u", torch.float32); _need(q_plain, "q_plain"); _need(q_full, "q_full"); _need(pages, "pages")
+    lib = _build.load("blocks")
+    _check("blocks", lib.jk_latent_qkv(
+        _ptr(u), _c_int(u.shape[1]), _c_int(q_off), _c_int(kv_off), _c_int(heads), _c_int(dn), _c_int(dr), _c_int(latent), _c_int(rot_dims),
+        _ptr(freq), _c_float(magnitude), _ptr(norm_weight), _c_float(eps), _ptr(positions), _ptr(row_req), _ptr(block_table),
+        _c_int(block_table.shape[1]), _c_int(page_size), _ptr(q_plain), _ptr(q_full), _ptr(pages), _c_int(dtype_code(pages.dtype)),
+        _c_int(u.shape[0]), _stream()))
+
+
+def head_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, out_head_stride: int, gate: Optional[torch.Tensor] = None,
+                gate_ld: int = 0) -> torch.Tensor:
+    """out[t, h, :n] = x[t, h] w[h]^T for ``w [heads, n, k]``, times sigmoid(gate[t, h n + j]) if given (float32 rows ``gate_ld`` apart)."""
+    _need(x, "x"); _need(w, "w"); _need(out, "out")
+    H, n, k = w.shape
+    lib = _build.load("blocks")
+    _check("blocks", lib.jk_head_linear(_ptr(x), _ptr(w), _ptr(out), _c_int(dtype_code(x.dtype)), _c_int(x.shape[0]), _c_int(H), _c_int(n),
+                                        _c_int(k), _c_int(out_head_stride), _ptr(gate), _c_int(gate_ld), _stream()))
+    return out
+
+
+def latent_attention(q: torch.Tensor, pages: torch.Tensor, out: torch.Tensor, positions, row_req, block_table, heads: int, latent: int,
+                     dr: int, scale: float, splits: int = 1) -> torch.Tensor:
+    """Causal attention of ``heads`` query heads ``[T, heads, latent + dr]`` over the paged rows ``[pages, page, latent + dr]``;
+    out ``[T, heads, latent]``.  ``splits`` > 1 cuts each row's keys into that many ranges."""
+    _need(q, "q"); _need(pages, "pages"); _need(out, "out")
+    T = q.shape[0]
+    lib = _build.load("blocks")
+    lib.jk_latent_attention_scratch.restype = ctypes.c_longlong
+    floats = lib.jk_latent_attention_scratch(_c_int(T), _c_int(heads), _c_int(latent), _c_int(splits))
+    part = torch.empty(max(int(floats), 1), dtype=torch.float32, device=q.device) if splits > 1 else None
+    _check("blocks", lib.jk_latent_attention(_ptr(q), _ptr(pages), _ptr(out), _ptr(part), _c_int(dtype_code(q.dtype)), _ptr(positions),
+                                             _ptr(row_req), _ptr(block_table), _c_int(block_table.shape[1]), _c_int(pages.shape[-2]),
+                                             _c_int(T), _c_int(heads), _c_int(latent), _c_int(dr), _c_float(scale), _c_int(splits), _stream()))
+    return out
+
+
+def causal_conv(u: torch.Tensor, off: int, channels: int, taps: torch.Tensor, bias: Optional[torch.Tensor], act: int,
+                tail: Optional[torch.Tensor], row_req, req_start, slot_ids, y32: Optional[torch.Tensor], yT: Optional[torch.Tensor]) -> None:
+    """y = act(bias + taps over time of u[:, off : off + channels]); the tails ``[slots, taps - 1, channels]`` move forward."""
+    _need(u, "u", torch.float32); _need(taps, "taps", torch.float32)
+    lib = _build.load("blocks")
+    _check("blocks", lib.jk_causal_conv(_ptr(u), _c_int(u.shape[1]), _c_int(off), _c_int(channels), _ptr(taps), _ptr(bias), _c_int(taps.shape[1]),
+                                        _c_int(act), _ptr(tail), _ptr(row_req), _ptr(req_start), _ptr(slot_ids), _ptr(y32), _ptr(yT),
+                                        _c_int(dtype_code(yT.dtype) if yT is not None else F32), _c_int(u.shape[0]),
+                                        _c_int(req_start.numel() - 1), _stream()))
+
+
+def selective_scan(x: torch.Tensor, low: torch.Tensor, dt_rank: int, states: int, z: torch.Tensor, z_ld: int, w_dt, dt_bias, A, skip,
+                   state: torch.Tensor, req_start, slot_ids, out: torch.Tensor) -> torch.Tensor:
+    """The selective scan of csrc/blocks.cu over each request's rows, from and into ``state [slots, channels, states]``."""
+    for t, n in ((x, "x"), (low, "low"), (w_dt, "w_dt"), (dt_bias, "dt_bias"), (A, "A"), (skip, "skip"), (state, "state")):
+        _need(t, n, torch.float32)
+    _need(z, "z", torch.float32, contiguous=False)
+    lib = _build.load("blocks")
+    _check("blocks", lib.jk_selective_scan(_ptr(x), _ptr(low), _c_int(low.shape[1]), _c_int(dt_rank), _c_int(states), _c_int(x.shape[1]),
+                                           _ptr(z), _c_int(z_ld), _ptr(w_dt), _ptr(dt_bias), _ptr(A), _ptr(skip), _ptr(state), _ptr(req_start),
+                                           _ptr(slot_ids), _c_int(req_start.numel() - 1), _ptr(out), _c_int(dtype_code(out.dtype)), _stream()))
+    return out
+
+
+def routed_experts(h: torch.Tensor, router: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, delta: torch.Tensor, add: bool,
+                   experts: int, top: int, act: int) -> torch.Tensor:
+    """delta (+)= sum over each row's ``top`` experts of largest sigmoid(router h) of expert(score * h); ``w_gate_up``
+    ``[experts * 2 ff, d]`` (an expert's gate rows, then its up rows), ``w_down [experts * d, ff]``."""
+    _need(h, "h"); _need(router, "router", torch.float32); _need(delta, "delta", torch.float32)
+    T, d = h.shape
+    ff = w_down.shape[1]
+    lib = _build.load("blocks")
+    lib.jk_routed_experts_workspace.restype = ctypes.c_longlong
+    route = torch.empty(int(lib.jk_routed_experts_workspace(_c_int(T), _c_int(experts), _c_int(top))), dtype=torch.int32, device=h.device)
+    act_buf = torch.empty(T * top, ff, dtype=h.dtype, device=h.device)
+    y = torch.empty(T * top, d, dtype=torch.float32, device=h.device)
+    _check("blocks", lib.jk_routed_experts(_ptr(h), _ptr(router), _ptr(w_gate_up), _ptr(w_down), _ptr(delta), _c_int(1 if add else 0),
+                                           _c_int(dtype_code(h.dtype)), _c_int(T), _c_int(d), _c_int(ff), _c_int(experts), _c_int(top),
+                                           _c_int(act), _ptr(route), _ptr(act_buf), _ptr(y), _stream()))
+    return delta
+
+
+def softcap(x: torch.Tensor, cap: float) -> torch.Tensor:
+    _need(x, "x", torch.float32)
+    lib = _build.load("blocks")
+    _check("blocks", lib.jk_softcap(_ptr(x), _c_float(cap), _c_ll(x.numel()), _stream()))
+    return x
+
+
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     _need(logits, "logits", torch.float32, contiguous=False); _need(out, "out", torch.int32)
     n, v = logits.shape
