@@ -257,6 +257,21 @@ def sitelorn_shape(width, ff, heads, kv_heads, dim, vocab, window, layers=8):
             "layers": order[:layers]}
 
 
+def vunelix_shape(width, ff, heads, dim, vocab):
+    """Seven layers, eight layer runs (the second layer runs twice): latent attention with plain heads of ``dim``, rotated
+    parts of dim / 2, values of ``dim`` and a latent vector of 4 dim; selective scans of 2 width channels with 16 states; a
+    dense feed-forward in the first layer, then eight experts of ff / 4 of which a row takes two, and a shared one."""
+    att = {"heads": heads, "dim": dim, "rot_dim": dim // 2, "vdim": dim, "kv_rank": 4 * dim, "scale": (dim + dim // 2) ** -0.5,
+           "rot": {"base": 1e4, "dims": dim // 2, "scaling": {"factor": 4.0, "original": 1024, "fast": 32.0, "slow": 1.0}}}
+    ssm = {"inner": 2 * width, "state": 16, "dt_rank": width // 16, "conv": 4}
+    moe = {"kind": "moe", "router": {"experts": 8, "top": 2}, "expert": {"ff": ff // 4}, "shared": {"ff": ff // 4}}
+    lat = lambda mlp: {"type": "latent_attention", "mixer": att, "mlp": mlp}
+    scan = {"type": "mamba1", "mixer": ssm, "mlp": moe}
+    return {"architecture": "Vunelix", "norm": {"eps": 1e-5}, "vocab": vocab, "width": width, "logit_softcap": 30.0,
+            "loop": {"start": 1, "stop": 2, "times": 2},
+            "layers": [lat({"kind": "dense", "ff": ff}), lat(moe), scan, lat(moe), lat(moe), scan, lat(moe)]}
+
+
 def decoder_shape(width, ff, heads, kv_heads, dim, vocab, layers=8):
     return dict(model_type="llama", num_hidden_layers=layers, hidden_size=width, num_attention_heads=heads, num_key_value_heads=kv_heads,
                 head_dim=dim, intermediate_size=ff, vocab_size=vocab, max_position_embeddings=4096, rms_norm_eps=1e-5,
@@ -287,15 +302,35 @@ def record_cost(op, T, B, context, decode, page_bytes):
         return T * op.n * (4 + 4 + 4 + 2), 0.0
     if kind == "cast":
         return T * op.n * 6, 0.0
+    if kind == "norm_add":
+        return T * op.n * (4 + 4 + 4 + 2), 0.0
+    if kind == "reinject":
+        return 2 * op.n * op.k + T * (8 * op.n + 2 * 2 * op.k + 8 * op.n), 2.0 * T * op.n * op.k
+    if kind == "latent_qkv":
+        return 4 * T * op.ld + 2 * T * (op.heads * (op.head_dim + op.rot_width) + op.rank + op.rot_width), 0.0
+    if kind == "head_linear":
+        return 2 * op.heads * op.n * op.k + 2 * T * op.heads * (op.k + op.n), 2.0 * T * op.heads * op.n * op.k
+    if kind == "latent_attention":
+        width = op.rank + op.rot_width
+        keys = B * context if decode else T
+        seen = (B * context) if decode else T * (T + 1) // 2
+        return keys * width * 2 + 2 * T * op.heads * (width + op.rank), 2.0 * seen * op.heads * (width + op.rank)
+    if kind == "causal_conv":
+        return T * op.n * (4 + 4 + 2), 2.0 * T * op.n * op.taps
+    if kind == "selective_scan":
+        return T * op.n * (4 + 4 + 2) + 4 * T * (op.rank + 2 * op.k) + 2 * B * op.n * op.k * 4, T * op.n * (6.0 * op.k + 2.0 * op.rank)
+    if kind == "experts":
+        used = min(op.experts, T * op.top)
+        return used * 3 * op.n * op.ff * 2 + T * op.n * (2 + 4) + T * op.top * (op.ff * 4 + op.n * 8), 2.0 * T * op.top * 3 * op.n * op.ff
     return 0, 0.0
 
 
 def run_design(args):
-    """Prefill and decode of the Sitelorn design at layer sizes of real models beside the decoder (llama graph) of the same
+    """Prefill and decode of another design (Sitelorn, Vunelix) at layer sizes of real models beside the decoder (llama graph) of the same
     width, feed-forward, heads and layer count, and every kind of launch record of both timed alone against its roofline.
     Prints one JSON line of its own kind; the default benchmark is untouched."""
     import torch
-    from infinicore_infer_b200.config import MiniCPMConfig, SitelornConfig
+    from infinicore_infer_b200.config import MiniCPMConfig, SitelornConfig, VunelixConfig
     from infinicore_infer_b200.engine import Engine, StepEntry
     from infinicore_infer_b200.parts import model_manifest
     from infinicore_infer_b200.parts.program import OP_NAMES
@@ -313,8 +348,10 @@ def run_design(args):
         for size in args.design_sizes.split(","):
             width, ff, heads, kv_heads, dim, vocab = DESIGN_SIZES[size]
             block = out["sizes"][size] = {"width": width, "ff": ff, "heads": heads, "kv_heads": kv_heads, "head_dim": dim, "layers": 8}
-            for which in ("sitelorn", "decoder"):
-                if which == "sitelorn":
+            for which in (args.design, "decoder"):
+                if which == "vunelix":
+                    cfg = VunelixConfig.from_dict(vunelix_shape(width, ff, heads, dim, vocab), max_tokens=max(4096, context + page))
+                elif which == "sitelorn":
                     cfg = SitelornConfig.from_dict(sitelorn_shape(width, ff, heads, kv_heads, dim, vocab, args.design_window),
                                                    max_tokens=max(4096, context + page))
                 else:
@@ -326,6 +363,8 @@ def run_design(args):
                 for view in engine.cache.views:
                     if hasattr(view, "k_pages"):
                         view.k_pages.normal_(0, 0.5); view.v_pages.normal_(0, 0.5)
+                    elif hasattr(view, "state") and view.state is not None and view.state.dtype == torch.float32:
+                        view.state.normal_(0, 0.1)
                 V = spec.vocab_size
                 res = block[which] = {}
                 # prefill: one prompt of T tokens, the best of three after a warm-up
@@ -378,7 +417,7 @@ def run_design(args):
                         if kind in ("embed",):
                             continue
                         op = prog.ops[i]
-                        key = f"{kind}:{op.n}x{op.k}" if kind in ("linear", "gate_up", "residual", "qkv") else \
+                        key = f"{kind}:{op.n}x{op.k}" if kind in ("linear", "gate_up", "residual", "qkv", "head_linear") else \
                             (f"{kind}:{'projected' if op.rank else 'constant'}" if kind == "linear_attention" else kind)
                         if not (op.wanted_rows and kind != "linear"):
                             names.setdefault(key, []).append(i)
@@ -393,7 +432,7 @@ def run_design(args):
                             nbytes, flops = record_cost(op, rows, nreq, pos + 1 if dec else T, dec, page)
                             row[phase + "_us"] = round(us, 2)
                             mem_frac = nbytes / (us * 1e-6) / 1e9 / peaks["hbm_gbs"]
-                            peak_f = F32_FMA_TFLOPS if OP_NAMES.get(op.kind) == "linear_attention" else peaks["bf16_tflops"]
+                            peak_f = F32_FMA_TFLOPS if OP_NAMES.get(op.kind) in ("linear_attention", "selective_scan", "causal_conv") else peaks["bf16_tflops"]
                             flop_frac = flops / (us * 1e-6) / 1e12 / peak_f
                             row[phase + "_frac"] = round(max(mem_frac, flop_frac), 4)
                             row[phase + "_bound"] = "memory" if mem_frac >= flop_frac else "compute"
@@ -425,7 +464,7 @@ def main():
                     help="run a few steps between cudaProfilerStart/Stop (for ncu --profile-from-start off) and exit")
     ap.add_argument("--shape", default="2b", choices=["2b", "1b", "8b"],
                     help="layer sizes: 2b is the headline configuration; the others are for profiles and side measurements")
-    ap.add_argument("--design", default=None, choices=["sitelorn"],
+    ap.add_argument("--design", default=None, choices=["sitelorn", "vunelix"],
                     help="instead of the benchmark: prefill and decode of this design at real layer sizes beside the decoder of equal size")
     ap.add_argument("--design-sizes", default="2k,4k", help="comma-separated names of " + ", ".join(sorted(DESIGN_SIZES)))
     ap.add_argument("--design-prompt", type=int, default=2048)

@@ -222,37 +222,53 @@ JK_EXPORT int jk_latent_qkv(const float *u, int ld, int q_off, int kv_off, int H
 }
 
 // ---------------------------------------------------------------------------------------------------------------
-// Tiled products on the CUDA cores: C[M, N] = A[M, K] W[N, K]^T with float32 accumulation in the order of K, operands
-// of type T.  A block of 256 threads makes a tile of 64 x 64, a thread 4 x 4 of it; K passes shared memory 16 at a time.
-// Rows of A may be picked through an index (a_rows).  With GLU a second weight tile W2 runs along and the epilogue sees
-// both sums.  Used per head (head_linear) and per expert (expert products), where the problem depends on the block.
+// Tiled products: C[M, N] = A[M, K] W[N, K]^T with float32 accumulation, operands of type T.  A block of 256 threads
+// makes a tile of 64 x 64.  float operands: on the CUDA cores (FFMA in the order of K, a thread 4 x 4 of the tile, K
+// through shared memory 16 at a time).  bfloat16 operands: on the tensor cores (mma.sync m16n8k16, a warp 16 x 32 of the
+// tile, K through shared memory 32 at a time, fragments by ldmatrix).  Rows of A may be picked through an index (a_rows).
+// With GLU a second weight tile W2 runs along and the epilogue sees both sums.  A thread holds 16 sums; tile_at() says
+// where sum e lies in the tile.  Used per head (head_linear) and per expert (expert products), where the problem depends
+// on the block.
 // ---------------------------------------------------------------------------------------------------------------
 constexpr int GT_M = 64, GT_N = 64, GT_K = 16;
 
-template <typename T, bool GLU>
-__device__ __forceinline__ void tile_product(const T *__restrict__ A, size_t lda, const int *__restrict__ a_rows, int M,
-                                             const T *__restrict__ W, const T *__restrict__ W2, size_t ldw, int N, int K, int m0, int n0,
-                                             float (&acc)[4][4], float (&acc2)[4][4]) {
+template <typename T> struct OnTensorCores { static constexpr bool value = false; };
+template <> struct OnTensorCores<__nv_bfloat16> { static constexpr bool value = true; };
+
+template <typename T>
+__device__ __forceinline__ void tile_at(int e, int *row, int *col) {
+    if (OnTensorCores<T>::value) {
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+        *row = (warp & 3) * 16 + (lane >> 2) + ((e & 2) ? 8 : 0);
+        *col = (warp >> 2) * 32 + (e >> 2) * 8 + (lane & 3) * 2 + (e & 1);
+    } else {
+        *row = (threadIdx.x / 16) * 4 + e / 4;
+        *col = (threadIdx.x % 16) * 4 + e % 4;
+    }
+}
+
+template <bool GLU>
+__device__ __forceinline__ void tile_product(const float *__restrict__ A, size_t lda, const int *__restrict__ a_rows, int M,
+                                             const float *__restrict__ W, const float *__restrict__ W2, size_t ldw, int N, int K, int m0, int n0,
+                                             float (&acc)[16], float (&acc2)[16]) {
     __shared__ float As[GT_K][GT_M + 4];
     __shared__ float Ws[GT_K][GT_N + 4];
     __shared__ float W2s[GLU ? GT_K : 1][GT_N + 4];
     const int tid = threadIdx.x, ty = tid / 16, tx = tid % 16;
     const int lr = tid / 4, lk = (tid % 4) * 4;      // this thread loads row lr, k lk .. lk + 3 of each operand tile
     const int am = m0 + lr, wn = n0 + lr;
-    const T *arow = am < M ? A + (size_t)(a_rows ? a_rows[am] : am) * lda : nullptr;
-    const T *wrow = wn < N ? W + (size_t)wn * ldw : nullptr;
-    const T *w2row = (GLU && wn < N) ? W2 + (size_t)wn * ldw : nullptr;
+    const float *arow = am < M ? A + (size_t)(a_rows ? a_rows[am] : am) * lda : nullptr;
+    const float *wrow = wn < N ? W + (size_t)wn * ldw : nullptr;
+    const float *w2row = (GLU && wn < N) ? W2 + (size_t)wn * ldw : nullptr;
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
-#pragma unroll
-        for (int j = 0; j < 4; ++j) { acc[i][j] = 0.f; acc2[i][j] = 0.f; }
+    for (int e = 0; e < 16; ++e) { acc[e] = 0.f; acc2[e] = 0.f; }
     for (int k0 = 0; k0 < K; k0 += GT_K) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const int k = k0 + lk + i;
-            As[lk + i][lr] = (arow && k < K) ? to_f32(arow[k]) : 0.f;
-            Ws[lk + i][lr] = (wrow && k < K) ? to_f32(wrow[k]) : 0.f;
-            if (GLU) W2s[lk + i][lr] = (w2row && k < K) ? to_f32(w2row[k]) : 0.f;
+            As[lk + i][lr] = (arow && k < K) ? arow[k] : 0.f;
+            Ws[lk + i][lr] = (wrow && k < K) ? wrow[k] : 0.f;
+            if (GLU) W2s[lk + i][lr] = (w2row && k < K) ? w2row[k] : 0.f;
         }
         __syncthreads();
 #pragma unroll
@@ -264,9 +280,81 @@ __device__ __forceinline__ void tile_product(const T *__restrict__ A, size_t lda
             for (int i = 0; i < 4; ++i)
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    acc[i][j] = fmaf(av[i], wv[j], acc[i][j]);
-                    if (GLU) acc2[i][j] = fmaf(av[i], w2v[j], acc2[i][j]);
+                    acc[i * 4 + j] = fmaf(av[i], wv[j], acc[i * 4 + j]);
+                    if (GLU) acc2[i * 4 + j] = fmaf(av[i], w2v[j], acc2[i * 4 + j]);
                 }
+        }
+        __syncthreads();
+    }
+}
+
+__device__ __forceinline__ void ldmatrix_x4(unsigned &r0, unsigned &r1, unsigned &r2, unsigned &r3, const void *smem_row) {
+    const unsigned addr = (unsigned)__cvta_generic_to_shared(smem_row);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];\n" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16_16816(float *d, unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+constexpr int TC_K = 32, TC_LD = TC_K + 8;     // rows of 80 bytes: 16-byte aligned for ldmatrix, and eight of them hit distinct banks
+
+// eight elements of a row from k on into shared memory; zeros beyond K or where there is no row
+__device__ __forceinline__ void stage8(__nv_bfloat16 *dst, const __nv_bfloat16 *row, int k, int K, bool vec) {
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (row != nullptr) {
+        if (vec && k + 8 <= K) {
+            v = *reinterpret_cast<const uint4 *>(row + k);
+        } else {
+            __nv_bfloat16 t[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) t[i] = k + i < K ? row[k + i] : __float2bfloat16_rn(0.f);
+            v = *reinterpret_cast<const uint4 *>(t);
+        }
+    }
+    *reinterpret_cast<uint4 *>(dst) = v;
+}
+
+template <bool GLU>
+__device__ __forceinline__ void tile_product(const __nv_bfloat16 *__restrict__ A, size_t lda, const int *__restrict__ a_rows, int M,
+                                             const __nv_bfloat16 *__restrict__ W, const __nv_bfloat16 *__restrict__ W2, size_t ldw, int N, int K,
+                                             int m0, int n0, float (&acc)[16], float (&acc2)[16]) {
+    __shared__ __align__(16) __nv_bfloat16 As[GT_M * TC_LD];
+    __shared__ __align__(16) __nv_bfloat16 Ws[GT_N * TC_LD];
+    __shared__ __align__(16) __nv_bfloat16 W2s[GLU ? GT_N * TC_LD : 8];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int lr = tid / 4, lk = (tid % 4) * 8;      // this thread stages row lr, k lk .. lk + 7 of each operand tile
+    const int am = m0 + lr, wn = n0 + lr;
+    const __nv_bfloat16 *arow = am < M ? A + (size_t)(a_rows ? a_rows[am] : am) * lda : nullptr;
+    const __nv_bfloat16 *wrow = wn < N ? W + (size_t)wn * ldw : nullptr;
+    const __nv_bfloat16 *w2row = (GLU && wn < N) ? W2 + (size_t)wn * ldw : nullptr;
+    const bool vec_a = lda % 8 == 0 && (uintptr_t)A % 16 == 0;
+    const bool vec_w = ldw % 8 == 0 && (uintptr_t)W % 16 == 0 && (!GLU || (uintptr_t)W2 % 16 == 0);
+#pragma unroll
+    for (int e = 0; e < 16; ++e) { acc[e] = 0.f; acc2[e] = 0.f; }
+    const int a_row = (warp & 3) * 16 + (lane & 15), a_col = (lane >> 4) * 8;
+    const int b_row = (warp >> 2) * 32 + (lane >> 4) * 8 + (lane & 7), b_col = ((lane >> 3) & 1) * 8;
+    for (int k0 = 0; k0 < K; k0 += TC_K) {
+        stage8(As + lr * TC_LD + lk, arow, k0 + lk, K, vec_a);
+        stage8(Ws + lr * TC_LD + lk, wrow, k0 + lk, K, vec_w);
+        if (GLU) stage8(W2s + lr * TC_LD + lk, w2row, k0 + lk, K, vec_w);
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < TC_K; kk += 16) {
+            unsigned a0, a1, a2, a3;
+            ldmatrix_x4(a0, a1, a2, a3, As + a_row * TC_LD + kk + a_col);
+#pragma unroll
+            for (int p = 0; p < 2; ++p) {          // two tiles of eight columns at a time
+                unsigned b0, b1, b2, b3;
+                ldmatrix_x4(b0, b1, b2, b3, Ws + (b_row + p * 16) * TC_LD + kk + b_col);
+                mma_bf16_16816(acc + (2 * p) * 4, a0, a1, a2, a3, b0, b1);
+                mma_bf16_16816(acc + (2 * p + 1) * 4, a0, a1, a2, a3, b2, b3);
+                if (GLU) {
+                    ldmatrix_x4(b0, b1, b2, b3, W2s + (b_row + p * 16) * TC_LD + kk + b_col);
+                    mma_bf16_16816(acc2 + (2 * p) * 4, a0, a1, a2, a3, b0, b1);
+                    mma_bf16_16816(acc2 + (2 * p + 1) * 4, a0, a1, a2, a3, b2, b3);
+                }
+            }
         }
         __syncthreads();
     }
@@ -279,21 +367,17 @@ __global__ void __launch_bounds__(256) head_linear_kernel(const T *__restrict__ 
     pdl_trigger();
     pdl_wait();
     const int h = blockIdx.z, m0 = blockIdx.x * GT_M, n0 = blockIdx.y * GT_N;
-    float acc[4][4], unused[4][4];
-    tile_product<T, false>(in + (size_t)h * K, (size_t)H * K, nullptr, rows, w + (size_t)h * N * K, nullptr, (size_t)K, N, K, m0, n0, acc, unused);
-    const int ty = threadIdx.x / 16, tx = threadIdx.x % 16;
+    float acc[16], unused[16];
+    tile_product<false>(in + (size_t)h * K, (size_t)H * K, nullptr, rows, w + (size_t)h * N * K, (const T *)nullptr, (size_t)K, N, K, m0, n0, acc, unused);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const int t = m0 + ty * 4 + i;
-        if (t >= rows) continue;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const int n = n0 + tx * 4 + j;
-            if (n >= N) continue;
-            float v = acc[i][j];
-            if (gate != nullptr) v *= sigmoid_f(gate[(size_t)t * gate_ld + (size_t)h * N + n]);
-            out[((size_t)t * H + h) * out_hs + n] = from_f32<T>(v);
-        }
+    for (int e = 0; e < 16; ++e) {
+        int r, c;
+        tile_at<T>(e, &r, &c);
+        const int t = m0 + r, n = n0 + c;
+        if (t >= rows || n >= N) continue;
+        float v = acc[e];
+        if (gate != nullptr) v *= sigmoid_f(gate[(size_t)t * gate_ld + (size_t)h * N + n]);
+        out[((size_t)t * H + h) * out_hs + n] = from_f32<T>(v);
     }
 }
 
@@ -761,19 +845,17 @@ __global__ void __launch_bounds__(256) expert_gate_up_kernel(const T *__restrict
     if (!expert_tile(starts, E, blockIdx.x, &e, &m0)) return;
     const int first = starts[e], M = starts[e + 1] - first, n0 = blockIdx.y * GT_N;
     const T *we = w + (size_t)e * 2 * ff * D;
-    float g[4][4], u[4][4];
-    tile_product<T, true>(h, (size_t)D, entry_row + first, M, we, we + (size_t)ff * D, (size_t)D, ff, D, m0, n0, g, u);
-    const int ty = threadIdx.x / 16, tx = threadIdx.x % 16;
+    float g[16], u[16];
+    tile_product<true>(h, (size_t)D, entry_row + first, M, we, we + (size_t)ff * D, (size_t)D, ff, D, m0, n0, g, u);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const int r = m0 + ty * 4 + i;
-        if (r >= M) continue;
+    for (int e = 0; e < 16; ++e) {
+        int r, c;
+        tile_at<T>(e, &r, &c);
+        r += m0;
+        const int n = n0 + c;
+        if (r >= M || n >= ff) continue;
         const float s = entry_score[first + r];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const int n = n0 + tx * 4 + j;
-            if (n < ff) act[(size_t)(first + r) * ff + n] = from_f32<T>(block_act(actf, s * g[i][j]) * (s * u[i][j]));
-        }
+        act[(size_t)(first + r) * ff + n] = from_f32<T>(block_act(actf, s * g[e]) * (s * u[e]));
     }
 }
 
@@ -786,18 +868,15 @@ __global__ void __launch_bounds__(256) expert_down_kernel(const T *__restrict__ 
     int e, m0;
     if (!expert_tile(starts, E, blockIdx.x, &e, &m0)) return;
     const int first = starts[e], M = starts[e + 1] - first, n0 = blockIdx.y * GT_N;
-    float acc[4][4], unused[4][4];
-    tile_product<T, false>(act + (size_t)first * ff, (size_t)ff, nullptr, M, w + (size_t)e * D * ff, nullptr, (size_t)ff, D, ff, m0, n0, acc, unused);
-    const int ty = threadIdx.x / 16, tx = threadIdx.x % 16;
+    float acc[16], unused[16];
+    tile_product<false>(act + (size_t)first * ff, (size_t)ff, nullptr, M, w + (size_t)e * D * ff, (const T *)nullptr, (size_t)ff, D, ff, m0, n0, acc, unused);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const int r = m0 + ty * 4 + i;
-        if (r >= M) continue;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const int n = n0 + tx * 4 + j;
-            if (n < D) y[(size_t)(first + r) * D + n] = acc[i][j];
-        }
+    for (int i = 0; i < 16; ++i) {
+        int r, c;
+        tile_at<T>(i, &r, &c);
+        r += m0;
+        const int n = n0 + c;
+        if (r < M && n < D) y[(size_t)(first + r) * D + n] = acc[i];
     }
 }
 

@@ -126,11 +126,16 @@ def dense_ff(h, W, p):
     return gated_unit(h, W, p, torch.relu)
 
 
-def routed_ff(h, mlp, W, p):
+def routed_ff(h, mlp, W, p, margins=None):
     """Each token goes to the ``top`` experts of largest sigmoid(router) score; an expert sees score * h; their outputs
-    add up, without renormalising, together with the shared expert's."""
+    add up, without renormalising, together with the shared expert's.  ``margins`` (a list) receives, per token, how far
+    the last chosen expert's router output lies above the first one left out."""
     n, top = int(mlp["router"]["experts"]), int(mlp["router"]["top"])
-    scores = torch.sigmoid(h @ W[p + "router"].T)
+    z = h @ W[p + "router"].T
+    scores = torch.sigmoid(z)
+    if margins is not None:
+        ranked = z.sort(dim=-1, descending=True).values
+        margins.append(ranked[:, top - 1] - ranked[:, top] if top < n else torch.full((h.shape[0],), math.inf, dtype=F))
     out = torch.zeros(h.shape[0], W[p + "e0.down"].shape[0], dtype=F)
     for t in range(h.shape[0]):
         for e in torch.topk(scores[t], top).indices.tolist():
@@ -154,8 +159,9 @@ def run_order(cfg):
     return order + [(i, None, False) for i in range(b, n)]
 
 
-def forward(tokens, cfg, W, return_layers=False):
-    """Logits [T, vocab] of one whole sequence; with ``return_layers`` also the stream after every layer run."""
+def forward(tokens, cfg, W, return_layers=False, margins=None):
+    """Logits [T, vocab] of one whole sequence; with ``return_layers`` also the stream after every layer run.  ``margins`` (a
+    list) receives one tensor [T] per routed feed-forward that ran (see ``routed_ff``)."""
     W = {k: (v.to(F) if v.is_floating_point() else v) for k, v in W.items()}
     eps = float(cfg["norm"]["eps"])
     x0 = W["embed"][torch.as_tensor(tokens, dtype=torch.long)]
@@ -177,7 +183,7 @@ def forward(tokens, cfg, W, return_layers=False):
         mlp = layer.get("mlp")
         if mlp is not None:
             h = rms_norm(x, W[p + "norm2"], eps)
-            d = dense_ff(h, W, p + "mlp.") if mlp["kind"] == "dense" else routed_ff(h, mlp, W, p + "mlp.")
+            d = dense_ff(h, W, p + "mlp.") if mlp["kind"] == "dense" else routed_ff(h, mlp, W, p + "mlp.", margins)
             x = x + rms_norm(d, W[p + "norm2b"], eps)
         seen.append(x.clone())
     logits = rms_norm(x, W["final.norm"], eps) @ W["embed"].T

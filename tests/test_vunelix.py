@@ -101,6 +101,14 @@ def engines(folders):
 
 
 _plain = {}
+# A row whose router leaves the last chosen expert this close (in the router's output) to the first one left out may go to
+# another expert once the activations are rounded to bfloat16: such a row's logits are those of another, equally valid,
+# choice, and are not compared.  (float32 reproduces every choice.)
+CLOSE_CALL = {"float32": 1e-4, "bfloat16": 0.08}
+
+
+class Expected(np.ndarray):
+    """Logits [T, vocab] with ``margin`` [T]: the smallest router margin of each row over the model's routed layers."""
 
 
 def expected(folders, name, seed, n):
@@ -108,7 +116,10 @@ def expected(folders, name, seed, n):
     if key not in _plain:
         _, cfg, w = folders[name]
         toks = random_tokens(seed, n, cfg["vocab"])
-        _plain[key] = (toks, plain.forward(toks, cfg, w).numpy())
+        margins = []
+        want = plain.forward(toks, cfg, w, margins=margins).numpy().view(Expected)
+        want.margin = torch.stack(margins).min(0).values.numpy() if margins else np.full(n, np.inf)
+        _plain[key] = (toks, want)
     return _plain[key]
 
 
@@ -122,8 +133,11 @@ def check(got, rid, want, tol, what):
     a small output into a large relative error now and then: one position in fifty may lie beyond ``tol``, none beyond three
     times it."""
     scale = np.abs(want).max()
-    errs = np.array([np.abs(got[(rid, p)].astype(np.float64) - want[p]).max() for p in range(len(want))])
     loose = tol > 1e-3
+    sure = getattr(want, "margin", np.full(len(want), np.inf)) >= CLOSE_CALL["bfloat16" if loose else "float32"]
+    assert len(want) < 20 or sure.sum() >= 0.7 * len(want), f"{what}: the router is sure of {int(sure.sum())} of {len(want)} rows only"
+    want = np.asarray(want)
+    errs = np.array([np.abs(got[(rid, p)].astype(np.float64) - want[p]).max() if sure[p] else 0.0 for p in range(len(want))])
     worst = int(errs.argmax())
     assert errs.max() <= (3 if loose else 1) * tol * scale, f"{what}: request {rid} position {worst}: error {errs.max():.3e} > {tol * scale:.3e}"
     if loose:
@@ -290,23 +304,26 @@ def test_queries_and_cache_rows_of_the_latent_attention(dtype):
         assert (row[:R] - c[r]).abs().max() < tol * c.abs().max() and (row[R:] - kr[r]).abs().max() < tol * kr.abs().max(), f"cache row of row {r}"
 
 
-@pytest.mark.parametrize("H,n,k", [(3, 40, 24), (1, 7, 130), (5, 65, 5)])
-def test_products_per_head_with_and_without_a_gate(H, n, k):
+@pytest.mark.parametrize("dtype", list(DTYPES))
+@pytest.mark.parametrize("H,n,k", [(3, 40, 24), (1, 7, 130), (5, 65, 5), (2, 128, 64)])
+def test_products_per_head_with_and_without_a_gate(H, n, k, dtype):
+    """float32 on the CUDA cores, bfloat16 on the tensor cores; sizes that are no multiple of a tile, of eight or of two."""
     from infinicore_infer_b200 import kernels as K
-    dev = torch.device("cuda:0")
+    dev, dt = torch.device("cuda:0"), DTYPES[dtype]
     g = torch.Generator().manual_seed(n)
-    for T in (1, 70):
-        x = torch.randn(T, H, k, generator=g, dtype=F)
-        w = torch.randn(H, n, k, generator=g, dtype=F)
+    tol = 1e-5 if dt == torch.float32 else 1e-2
+    for T in (1, 70, 133):
+        x = torch.randn(T, H, k, generator=g).to(dt).double()
+        w = torch.randn(H, n, k, generator=g).to(dt).double()
         gate = torch.randn(T, H * n + 3, generator=g, dtype=F)
         want = torch.einsum("thk,hnk->thn", x, w)
-        out = torch.zeros(T, H, n + 2, dtype=torch.float32, device=dev)
-        K.head_linear(x.float().to(dev), w.float().to(dev), out, n + 2)
-        assert (out[..., :n].double().cpu() - want).abs().max() < 1e-5 * want.abs().max() and torch.all(out[..., n:] == 0)
-        gated = torch.empty(T, H, n, dtype=torch.float32, device=dev)
-        K.head_linear(x.float().to(dev), w.float().to(dev), gated, n, gate=gate.float().to(dev), gate_ld=H * n + 3)
-        want_g = want * torch.sigmoid(gate[:, :H * n]).view(T, H, n)
-        assert (gated.double().cpu() - want_g).abs().max() < 1e-5 * want.abs().max()
+        out = torch.zeros(T, H, n + 2, dtype=dt, device=dev)
+        K.head_linear(x.to(dt).to(dev), w.to(dt).to(dev), out, n + 2)
+        assert (out[..., :n].double().cpu() - want).abs().max() < tol * want.abs().max() and torch.all(out[..., n:] == 0)
+        gated = torch.empty(T, H, n, dtype=dt, device=dev)
+        K.head_linear(x.to(dt).to(dev), w.to(dt).to(dev), gated, n, gate=gate.float().to(dev), gate_ld=H * n + 3)
+        want_g = want * torch.sigmoid(gate.float().double()[:, :H * n]).view(T, H, n)
+        assert (gated.double().cpu() - want_g).abs().max() < tol * want.abs().max()
 
 
 @pytest.mark.parametrize("E,N,K_,J", [(80, 5, 3, 3), (37, 24, 12, 4), (8, 70, 1, 2), (130, 16, 9, 1)])
