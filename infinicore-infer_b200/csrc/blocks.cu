@@ -22,6 +22,7 @@
 #include "common.cuh"
 
 #include <algorithm>
+#include <cstdlib>
 
 JK_DEFINE_ERROR_BUFFER(jk_blocks)
 
@@ -528,14 +529,217 @@ __global__ void latent_merge_kernel(const float *__restrict__ part, T *__restric
     }
 }
 
+// The same attention on the tensor cores (bfloat16, mma.sync m16n8k16 with float32 accumulation).  Since every head reads
+// the same cached rows, (query row, head) pairs are the M side of the products: a block of eight warps takes 32 pairs of
+// one request (RT rows x HT heads) and walks the request's cached rows 32 at a time through shared memory.  Warp (mw, nw)
+// has pairs mw * 16 .. + 15; for the scores it takes the tile's keys nw * 8 .. + 7 over the whole row width, the four nw
+// warps exchange scores through shared memory, every thread forms the softmax weights of its own fragment (float32; the
+// maximum and the sum go around the four lanes that share a row), and for the weighted sum it owns the output columns
+// nw * NT * 8 .. of all 32 keys, the cached tile serving as the value operand through ldmatrix.trans.  Ranges as above.
+constexpr int LT_PAIRS = 32, LT_KEYS = 32;
+
+struct LatentTcArgs {
+    const __nv_bfloat16 *q, *pages;
+    __nv_bfloat16 *out;
+    float *part;
+    const int *positions, *req_start, *block_table;
+    int nreq, H, R, dr, page_size, max_blocks, splits, HT, RT, ldk;
+    float scale;
+};
+
+__device__ __forceinline__ void ldmatrix_x2(unsigned &r0, unsigned &r1, const void *smem_row) {
+    const unsigned addr = (unsigned)__cvta_generic_to_shared(smem_row);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0, %1}, [%2];\n" : "=r"(r0), "=r"(r1) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned &r0, unsigned &r1, unsigned &r2, unsigned &r3, const void *smem_row) {
+    const unsigned addr = (unsigned)__cvta_generic_to_shared(smem_row);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];\n" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const unsigned *>(&v);
+}
+
+template <int NT>       // tiles of eight output columns per warp
+__global__ void __launch_bounds__(256) latent_attention_tc_kernel(LatentTcArgs a) {
+    pdl_trigger();
+    pdl_wait();
+    extern __shared__ __align__(16) unsigned char lt_smem[];
+    // the block's request and rows
+    int req = -1, t0 = 0, nrows = 0;
+    {
+        int tiles = 0;
+        for (int i = 0; i < a.nreq; ++i) {
+            const int len = a.req_start[i + 1] - a.req_start[i];
+            const int mine = (len + a.RT - 1) / a.RT;
+            if ((int)blockIdx.x < tiles + mine) {
+                const int local = ((int)blockIdx.x - tiles) * a.RT;
+                req = i; t0 = a.req_start[i] + local; nrows = min(a.RT, len - local);
+                break;
+            }
+            tiles += mine;
+        }
+    }
+    if (req < 0) return;
+    const int h0 = blockIdx.y * a.HT;
+    const int D = a.R + a.dr, DP = (D + 15) / 16 * 16, LDK = a.ldk, LDQ = DP + 8;
+    __nv_bfloat16 *Qs = reinterpret_cast<__nv_bfloat16 *>(lt_smem);                 // [32][LDQ]
+    __nv_bfloat16 *Ks = Qs + LT_PAIRS * LDQ;                                        // [32][LDK]
+    float *Sb = reinterpret_cast<float *>(Ks + LT_KEYS * LDK);                      // [2][16][33]
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, mw = warp & 1, nw = warp >> 1;
+    for (int idx = tid; idx < LT_PAIRS * LDQ; idx += 256) {
+        const int p = idx / LDQ, e = idx % LDQ, r = p / a.HT, h = h0 + p % a.HT;
+        float v = 0.f;
+        if (r < nrows && h < a.H && e < D) v = __bfloat162float(a.q[((size_t)(t0 + r) * a.H + h) * D + e]);
+        Qs[idx] = __float2bfloat16_rn(v);
+    }
+    const int max_pos = a.positions[t0 + nrows - 1];
+    int lo = 0, hi = max_pos + 1;
+    if (a.splits > 1) {
+        const int chunk = (((max_pos + a.splits) / a.splits) + 31) / 32 * 32;
+        lo = blockIdx.z * chunk;
+        hi = min(max_pos + 1, lo + chunk);
+    }
+    // this thread's two rows of its warp's 16 pairs
+    const int pa = mw * 16 + (lane >> 2), pb = pa + 8;
+    const int ra = pa / a.HT, rb = pb / a.HT, ha = h0 + pa % a.HT, hb = h0 + pb % a.HT;
+    const bool va = ra < nrows && ha < a.H, vb = rb < nrows && hb < a.H;
+    const int pos_a = va ? a.positions[t0 + ra] : -1, pos_b = vb ? a.positions[t0 + rb] : -1;
+    float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
+    float o[NT][4];
+#pragma unroll
+    for (int i = 0; i < NT; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+    const int *bt = a.block_table + (size_t)req * a.max_blocks;
+    const bool vec = D % 8 == 0 && (uintptr_t)a.pages % 16 == 0;
+    const int c8n = LDK / 8;
+    for (int j0 = lo; j0 < hi; j0 += LT_KEYS) {
+        const int n = min(LT_KEYS, hi - j0);
+        for (int idx = tid; idx < LT_KEYS * c8n; idx += 256) {
+            const int r = idx / c8n, c = (idx % c8n) * 8;
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (r < n && c < D) {
+                const int j = j0 + r;
+                const __nv_bfloat16 *src = a.pages + ((size_t)bt[j / a.page_size] * a.page_size + (size_t)(j % a.page_size)) * D + c;
+                if (vec && c + 8 <= D) {
+                    v = *reinterpret_cast<const uint4 *>(src);
+                } else {
+                    __nv_bfloat16 tmp[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) tmp[i] = c + i < D ? src[i] : __float2bfloat16_rn(0.f);
+                    v = *reinterpret_cast<const uint4 *>(tmp);
+                }
+            }
+            *reinterpret_cast<uint4 *>(Ks + r * LDK + c) = v;
+        }
+        __syncthreads();
+        // scores of this warp's pairs against the keys nw * 8 .. + 7
+        float s[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int kk = 0; kk < DP; kk += 16) {
+            unsigned a0, a1, a2, a3, b0, b1;
+            ldmatrix_x4(a0, a1, a2, a3, Qs + (mw * 16 + (lane & 15)) * LDQ + kk + (lane >> 4) * 8);
+            ldmatrix_x2(b0, b1, Ks + (nw * 8 + (lane & 7)) * LDK + kk + ((lane >> 3) & 1) * 8);
+            mma_bf16_16816(s, a0, a1, a2, a3, b0, b1);
+        }
+        {
+            float *row_a = Sb + (mw * 16 + (lane >> 2)) * 33, *row_b = row_a + 8 * 33;
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                const int k = nw * 8 + (lane & 3) * 2 + c, j = j0 + k;
+                row_a[k] = (k < n && j <= pos_a) ? s[c] * a.scale : -INFINITY;
+                row_b[k] = (k < n && j <= pos_b) ? s[2 + c] * a.scale : -INFINITY;
+            }
+        }
+        __syncthreads();
+        // softmax weights of this thread's fragment: keys (lane & 3) * 2 + {0, 1} + {0, 8, 16, 24} of its two rows
+        float pa_[8], pb_[8];
+        {
+            const float *row_a = Sb + (mw * 16 + (lane >> 2)) * 33, *row_b = row_a + 8 * 33;
+            float mx_a = -INFINITY, mx_b = -INFINITY;
+#pragma unroll
+            for (int g = 0; g < 4; ++g)
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    const int k = g * 8 + (lane & 3) * 2 + c;
+                    pa_[g * 2 + c] = row_a[k]; pb_[g * 2 + c] = row_b[k];
+                    mx_a = fmaxf(mx_a, pa_[g * 2 + c]); mx_b = fmaxf(mx_b, pb_[g * 2 + c]);
+                }
+            mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1)); mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
+            mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1)); mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
+            const float mn_a = fmaxf(m_a, mx_a), mn_b = fmaxf(m_b, mx_b);
+            const float corr_a = mn_a == -INFINITY ? 1.f : expf(m_a - mn_a), corr_b = mn_b == -INFINITY ? 1.f : expf(m_b - mn_b);
+            float sum_a = 0.f, sum_b = 0.f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                pa_[i] = mn_a == -INFINITY ? 0.f : expf(pa_[i] - mn_a);
+                pb_[i] = mn_b == -INFINITY ? 0.f : expf(pb_[i] - mn_b);
+                sum_a += pa_[i]; sum_b += pb_[i];
+            }
+            sum_a += __shfl_xor_sync(0xffffffffu, sum_a, 1); sum_a += __shfl_xor_sync(0xffffffffu, sum_a, 2);
+            sum_b += __shfl_xor_sync(0xffffffffu, sum_b, 1); sum_b += __shfl_xor_sync(0xffffffffu, sum_b, 2);
+            l_a = l_a * corr_a + sum_a; l_b = l_b * corr_b + sum_b;
+            m_a = mn_a; m_b = mn_b;
+#pragma unroll
+            for (int i = 0; i < NT; ++i) { o[i][0] *= corr_a; o[i][1] *= corr_a; o[i][2] *= corr_b; o[i][3] *= corr_b; }
+        }
+        // weighted sum: keys 0 .. 15, then 16 .. 31; values = the cached rows' columns nw * NT * 8 ..
+#pragma unroll
+        for (int ks = 0; ks < 2; ++ks) {
+            const unsigned a0 = pack_bf16(pa_[ks * 4 + 0], pa_[ks * 4 + 1]), a1 = pack_bf16(pb_[ks * 4 + 0], pb_[ks * 4 + 1]);
+            const unsigned a2 = pack_bf16(pa_[ks * 4 + 2], pa_[ks * 4 + 3]), a3 = pack_bf16(pb_[ks * 4 + 2], pb_[ks * 4 + 3]);
+#pragma unroll
+            for (int i = 0; i < NT; i += 2) {
+                unsigned b0, b1, b2, b3;
+                ldmatrix_x4_trans(b0, b1, b2, b3, Ks + (ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDK + (nw * NT + i) * 8 + (lane >> 4) * 8);
+                mma_bf16_16816(o[i], a0, a1, a2, a3, b0, b1);
+                mma_bf16_16816(o[i + 1], a0, a1, a2, a3, b2, b3);
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const bool valid = half ? vb : va;
+        if (!valid) continue;
+        const int t = t0 + (half ? rb : ra), h = half ? hb : ha;
+        const float l = half ? l_b : l_a, m = half ? m_b : m_a;
+        if (a.splits > 1) {
+            float *p = a.part + (((size_t)t * a.H + h) * a.splits + blockIdx.z) * (a.R + 2);
+#pragma unroll
+            for (int i = 0; i < NT; ++i)
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    const int col = (nw * NT + i) * 8 + (lane & 3) * 2 + c;
+                    if (col < a.R) p[col] = o[i][half * 2 + c];
+                }
+            if (nw == 0 && (lane & 3) == 0) { p[a.R] = m; p[a.R + 1] = l; }
+        } else {
+            __nv_bfloat16 *orow = a.out + ((size_t)t * a.H + h) * a.R;
+            const float inv = 1.f / l;
+#pragma unroll
+            for (int i = 0; i < NT; ++i)
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    const int col = (nw * NT + i) * 8 + (lane & 3) * 2 + c;
+                    if (col < a.R) orow[col] = __float2bfloat16_rn(o[i][half * 2 + c] * inv);
+                }
+        }
+    }
+}
+
+static bool latent_tc_enabled() {
+    static const bool on = [] { const char *e = std::getenv("JK_LATENT_NO_TC"); return !(e && e[0] == '1'); }();
+    return on;
+}
+
 // floats of `part` that `splits` ranges of T rows need
 JK_EXPORT long long jk_latent_attention_scratch(int T, int H, int R, int splits) {
     return splits > 1 ? (long long)T * H * splits * (R + 2) : 0;
 }
 
+// `req_start` [nreq + 1] (may be null): with it, bfloat16 rows go to the tensor-core kernel (latent sizes up to 512).
 JK_EXPORT int jk_latent_attention(const void *q, const void *pages, void *out, float *part, int dtype, const int *positions,
                                   const int *row_req, const int *block_table, int max_blocks, int page_size, int T, int H, int R,
-                                  int dr, float scale, int splits, cudaStream_t stream) {
+                                  int dr, float scale, int splits, const int *req_start, int nreq, cudaStream_t stream) {
     if (T == 0) return JK_OK;
     JK_REQUIRE(q && pages && out && positions && row_req && block_table, "latent_attention: an argument is missing");
     JK_REQUIRE(H > 0 && R > 0 && dr >= 0 && page_size > 0 && max_blocks > 0, "latent_attention: heads %d, latent %d + %d", H, R, dr);
@@ -544,8 +748,34 @@ JK_EXPORT int jk_latent_attention(const void *q, const void *pages, void *out, f
     if (splits < 1) splits = 1;
     JK_REQUIRE(splits == 1 || part != nullptr, "latent_attention: split keys need room for their parts");
     JK_REQUIRE(splits <= 65535, "latent_attention: %d ranges", splits);
-    LatentAttnArgs a{q, pages, out, part, positions, row_req, block_table, T, H, R, dr, page_size, max_blocks, splits, scale};
     const int D = R + dr;
+    if (dtype == JK_BF16 && req_start != nullptr && nreq > 0 && R <= 512 && latent_tc_enabled()) {
+        int HT = 1;
+        while (HT * 2 <= std::min(H, LT_PAIRS)) HT *= 2;
+        const int RT = LT_PAIRS / HT, tiles8 = (R + 7) / 8, per = (tiles8 + 3) / 4;
+        const int NT = per <= 2 ? 2 : (per <= 4 ? 4 : (per <= 8 ? 8 : 16));
+        const int DP = (D + 15) / 16 * 16, ldk = std::max(DP, 4 * NT * 8) + 8;
+        LatentTcArgs ta{(const __nv_bfloat16 *)q, (const __nv_bfloat16 *)pages, (__nv_bfloat16 *)out, part, positions, req_start, block_table,
+                        nreq, H, R, dr, page_size, max_blocks, splits, HT, RT, ldk, scale};
+        const size_t smem_tc = (size_t)LT_PAIRS * (DP + 8) * 2 + (size_t)LT_KEYS * ldk * 2 + 2 * 16 * 33 * sizeof(float);
+        dim3 grid((T + RT - 1) / RT + nreq, (H + HT - 1) / HT, splits);
+        JK_REQUIRE(grid.y <= 65535, "latent_attention: %d heads", H);
+#define LAUNCH_TC(NT_)                                                                                                                       \
+    do {                                                                                                                                    \
+        if (smem_tc > 48 * 1024) cudaFuncSetAttribute(latent_attention_tc_kernel<NT_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_tc); \
+        jk_launch(latent_attention_tc_kernel<NT_>, grid, dim3(256), smem_tc, stream, ta);                                                   \
+    } while (0)
+        if (NT == 2) LAUNCH_TC(2); else if (NT == 4) LAUNCH_TC(4); else if (NT == 8) LAUNCH_TC(8); else LAUNCH_TC(16);
+#undef LAUNCH_TC
+        JK_CHECK_LAUNCH("latent_attention_tc");
+        if (splits > 1) {
+            const int n = T * H;
+            jk_launch(latent_merge_kernel<__nv_bfloat16>, dim3((n + 3) / 4), dim3(128), 0, stream, (const float *)part, (__nv_bfloat16 *)out, n, R, splits);
+            JK_CHECK_LAUNCH("latent_merge");
+        }
+        return JK_OK;
+    }
+    LatentAttnArgs a{q, pages, out, part, positions, row_req, block_table, T, H, R, dr, page_size, max_blocks, splits, scale};
     const size_t smem = ((size_t)LA_WARPS * D + 32 * (size_t)(D + 1)) * sizeof(float);
     JK_REQUIRE(smem <= 220 * 1024, "latent_attention: rows of %d elements do not fit shared memory", D);
     dim3 grid((H + LA_WARPS - 1) / LA_WARPS, T, splits);

@@ -559,7 +559,7 @@ int run_latent_attention(Run &r, const RunnerOp &op) {
     if (splits > 1)
         if (int rc = r.slot(SLOT_DECODE, 4 * g_fns.latent_attention_scratch(T, H, op.rank, splits), &part, "the ranges of a latent attention")) return rc;
     RUN(blocks, g_fns.latent_attention(q, op.k_pages, o, (float *)part, r.env.dtype, r.st.positions, r.st.row_req, table, r.env.max_blocks,
-                                       r.env.page_size, T, H, op.rank, op.rot_width, op.softmax_scale, splits, r.stream));
+                                       r.env.page_size, T, H, op.rank, op.rot_width, op.softmax_scale, splits, r.st.req_start, r.st.nreq, r.stream));
     if (splits > 1) ++g_launches;
     return JK_OK;
 }

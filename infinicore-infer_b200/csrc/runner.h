@@ -65,7 +65,7 @@ typedef int (*LatentQkvFn)(const float *, int, int, int, int, int, int, int, int
                            const int *, const int *, int, int, void *, void *, void *, int, int, cudaStream_t);
 typedef int (*HeadLinearFn)(const void *, const void *, void *, int, int, int, int, int, int, const float *, int, cudaStream_t);
 typedef int (*LatentAttentionFn)(const void *, const void *, void *, float *, int, const int *, const int *, const int *, int, int, int,
-                                 int, int, int, float, int, cudaStream_t);
+                                 int, int, int, float, int, const int *, int, cudaStream_t);
 typedef long long (*LatentScratchFn)(int, int, int, int);
 typedef int (*CausalConvFn)(const float *, int, int, int, const float *, const float *, int, int, float *, const int *, const int *,
                             const int *, float *, void *, int, int, int, cudaStream_t);

@@ -686,9 +686,10 @@ def head_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, out_head_st
 
 
 def latent_attention(q: torch.Tensor, pages: torch.Tensor, out: torch.Tensor, positions, row_req, block_table, heads: int, latent: int,
-                     dr: int, scale: float, splits: int = 1) -> torch.Tensor:
+                     dr: int, scale: float, splits: int = 1, req_start: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Causal attention of ``heads`` query heads ``[T, heads, latent + dr]`` over the paged rows ``[pages, page, latent + dr]``;
-    out ``[T, heads, latent]``.  ``splits`` > 1 cuts each row's keys into that many ranges."""
+    out ``[T, heads, latent]``.  ``splits`` > 1 cuts each row's keys into that many ranges.  With ``req_start`` (int32, the first
+    row of each request and the row count) bfloat16 rows run on the tensor cores."""
     _need(q, "q"); _need(pages, "pages"); _need(out, "out")
     T = q.shape[0]
     lib = _build.load("blocks")
@@ -697,7 +698,8 @@ def latent_attention(q: torch.Tensor, pages: torch.Tensor, out: torch.Tensor, po
     part = torch.empty(max(int(floats), 1), dtype=torch.float32, device=q.device) if splits > 1 else None
     _check("blocks", lib.jk_latent_attention(_ptr(q), _ptr(pages), _ptr(out), _ptr(part), _c_int(dtype_code(q.dtype)), _ptr(positions),
                                              _ptr(row_req), _ptr(block_table), _c_int(block_table.shape[1]), _c_int(pages.shape[-2]),
-                                             _c_int(T), _c_int(heads), _c_int(latent), _c_int(dr), _c_float(scale), _c_int(splits), _stream()))
+                                             _c_int(T), _c_int(heads), _c_int(latent), _c_int(dr), _c_float(scale), _c_int(splits), _ptr(req_start),
+                                             _c_int(req_start.numel() - 1 if req_start is not None else 0), _stream()))
     return out
 
 

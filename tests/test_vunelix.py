@@ -241,7 +241,7 @@ def scrambled_pages(rows, page, dev, dtype, spare=2):
 def test_latent_attention_finds_one_far_key_at_any_place(dtype, H, R, dr, page):
     """Among hundreds of cached rows one far row gets a score that stands out, for queries in a prompt and for a single
     decoded row, with the far row at a page's first place, its last place, at position 0 and right before the query;
-    whole keys and keys cut into ranges agree."""
+    whole keys and keys cut into ranges agree.  float32 runs on the CUDA cores, bfloat16 on the tensor cores."""
     from infinicore_infer_b200 import kernels as K
     dev, dt = torch.device("cuda:0"), DTYPES[dtype]
     g = torch.Generator().manual_seed(H + R)
@@ -261,13 +261,14 @@ def test_latent_attention_finds_one_far_key_at_any_place(dtype, H, R, dr, page):
     tol = 2e-5 if dt == torch.float32 else 2e-2
     for splits in (1, 3, 7):
         out = torch.empty(T, H, R, dtype=dt, device=dev)
-        K.latent_attention(q.to(dt).to(dev).contiguous(), pages, out, pos, torch.zeros_like(pos), table, H, R, dr, 1.0, splits=splits)
+        starts = torch.tensor([0, T], dtype=torch.int32, device=dev)
+        K.latent_attention(q.to(dt).to(dev).contiguous(), pages, out, pos, torch.zeros_like(pos), table, H, R, dr, 1.0, splits=splits, req_start=starts)
         err = (out.double().cpu() - want).abs().max().item()
         assert err <= tol * want.abs().max().item(), f"prompt rows, {splits} ranges: {err}"
         for i in far:                             # the same rows one by one, as a decode step sees them
             one = torch.empty(1, H, R, dtype=dt, device=dev)
             K.latent_attention(q[i:i + 1].to(dt).to(dev).contiguous(), pages, one, pos[i:i + 1], torch.zeros(1, dtype=torch.int32, device=dev),
-                               table, H, R, dr, 1.0, splits=splits)
+                               table, H, R, dr, 1.0, splits=splits, req_start=torch.tensor([0, 1], dtype=torch.int32, device=dev))
             assert (one.double().cpu()[0] - want[i]).abs().max().item() <= tol * want.abs().max().item(), f"decoded row {i}, {splits} ranges"
     for i, j in far.items() if D >= 40 else ():   # the far row decides head 0's output
         assert (want[i, 0] - rows[j, :R]).abs().max() < 0.05 * rows[j, :R].abs().max() + 0.02
