@@ -300,8 +300,8 @@ __device__ __forceinline__ void mma_bf16_16816(float *d, unsigned a0, unsigned a
 
 constexpr int TC_K = 32, TC_LD = TC_K + 8;     // rows of 80 bytes: 16-byte aligned for ldmatrix, and eight of them hit distinct banks
 
-// eight elements of a row from k on into shared memory; zeros beyond K or where there is no row
-__device__ __forceinline__ void stage8(__nv_bfloat16 *dst, const __nv_bfloat16 *row, int k, int K, bool vec) {
+// eight elements of a row from k on; zeros beyond K or where there is no row
+__device__ __forceinline__ uint4 fetch8(const __nv_bfloat16 *row, int k, int K, bool vec) {
     uint4 v = make_uint4(0u, 0u, 0u, 0u);
     if (row != nullptr) {
         if (vec && k + 8 <= K) {
@@ -313,7 +313,7 @@ __device__ __forceinline__ void stage8(__nv_bfloat16 *dst, const __nv_bfloat16 *
             v = *reinterpret_cast<const uint4 *>(t);
         }
     }
-    *reinterpret_cast<uint4 *>(dst) = v;
+    return v;
 }
 
 template <bool GLU>
@@ -335,11 +335,18 @@ __device__ __forceinline__ void tile_product(const __nv_bfloat16 *__restrict__ A
     for (int e = 0; e < 16; ++e) { acc[e] = 0.f; acc2[e] = 0.f; }
     const int a_row = (warp & 3) * 16 + (lane & 15), a_col = (lane >> 4) * 8;
     const int b_row = (warp >> 2) * 32 + (lane >> 4) * 8 + (lane & 7), b_col = ((lane >> 3) & 1) * 8;
+    // the next tile's operands are asked for while this tile's products run
+    uint4 ra = fetch8(arow, lk, K, vec_a), rw = fetch8(wrow, lk, K, vec_w), rw2 = GLU ? fetch8(w2row, lk, K, vec_w) : make_uint4(0u, 0u, 0u, 0u);
     for (int k0 = 0; k0 < K; k0 += TC_K) {
-        stage8(As + lr * TC_LD + lk, arow, k0 + lk, K, vec_a);
-        stage8(Ws + lr * TC_LD + lk, wrow, k0 + lk, K, vec_w);
-        if (GLU) stage8(W2s + lr * TC_LD + lk, w2row, k0 + lk, K, vec_w);
+        *reinterpret_cast<uint4 *>(As + lr * TC_LD + lk) = ra;
+        *reinterpret_cast<uint4 *>(Ws + lr * TC_LD + lk) = rw;
+        if (GLU) *reinterpret_cast<uint4 *>(W2s + lr * TC_LD + lk) = rw2;
         __syncthreads();
+        if (k0 + TC_K < K) {
+            ra = fetch8(arow, k0 + TC_K + lk, K, vec_a);
+            rw = fetch8(wrow, k0 + TC_K + lk, K, vec_w);
+            if (GLU) rw2 = fetch8(w2row, k0 + TC_K + lk, K, vec_w);
+        }
 #pragma unroll
         for (int kk = 0; kk < TC_K; kk += 16) {
             unsigned a0, a1, a2, a3;
@@ -889,7 +896,7 @@ JK_EXPORT int jk_causal_conv(const float *u, int ld, int off, int C, const float
 // the states part, part + 8, ... in registers and a share of the K products; sums go around by shuffles.  A block of 256
 // threads owns 32 channels of one request and walks the request's rows.
 // ---------------------------------------------------------------------------------------------------------------
-constexpr int SS_LANES = 8;
+constexpr int SS_LANES = 8, SS_CHANNELS = 256 / SS_LANES, SS_CHUNK = 32;
 
 struct ScanArgs {
     const float *x;         // [T, E] after convolution and activation
@@ -901,15 +908,39 @@ struct ScanArgs {
     float *state;
     const int *req_start, *slot_ids;
     void *out;
+    const float *dt;        // step sizes made ahead, dt[t * ld_dt + c], or null: they are formed while the rows are staged
+    int ld_dt;
 };
 
+// dt[t, c] = softplus(low[t, :K] . Wdt[c] + bdt[c]) for a step of many rows: a float32 product on the CUDA cores
+__global__ void __launch_bounds__(256) scan_steps_kernel(const float *__restrict__ low, int ld_low, const float *__restrict__ Wdt,
+                                                         const float *__restrict__ bdt, float *__restrict__ dt, int ld_dt, int rows, int E, int K) {
+    pdl_trigger();
+    pdl_wait();
+    const int m0 = blockIdx.x * GT_M, n0 = blockIdx.y * GT_N;
+    float acc[16], unused[16];
+    tile_product<false>(low, (size_t)ld_low, nullptr, rows, Wdt, (const float *)nullptr, (size_t)K, E, K, m0, n0, acc, unused);
+#pragma unroll
+    for (int e = 0; e < 16; ++e) {
+        int r, c;
+        tile_at<float>(e, &r, &c);
+        const int t = m0 + r, ch = n0 + c;
+        if (t < rows && ch < E) dt[(size_t)t * ld_dt + ch] = softplus_f(acc[e] + bdt[ch]);
+    }
+}
+
+// Rows pass shared memory SS_CHUNK at a time (step sizes, inputs, B and C staged by all threads), so a row of the
+// recurrence costs no global load; a chunk's outputs leave together, times silu(z).
 template <typename T, int NPER>
 __global__ void __launch_bounds__(256) selective_scan_kernel(ScanArgs a) {
     pdl_trigger();
     pdl_wait();
+    extern __shared__ float ss_smem[];
+    float *s_dt = ss_smem, *s_x = s_dt + SS_CHUNK * SS_CHANNELS, *s_y = s_x + SS_CHUNK * SS_CHANNELS;
+    float *s_B = s_y + SS_CHUNK * SS_CHANNELS, *s_C = s_B + SS_CHUNK * a.N;
     const int req = blockIdx.y;
-    const int part = threadIdx.x % SS_LANES;
-    const int c = blockIdx.x * (256 / SS_LANES) + threadIdx.x / SS_LANES;
+    const int part = threadIdx.x % SS_LANES, cl = threadIdx.x / SS_LANES;
+    const int c0 = blockIdx.x * SS_CHANNELS, c = c0 + cl;
     const bool live = c < a.E;
     const int cc = live ? c : a.E - 1;          // idle lanes follow a real channel so that the shuffles stay whole
     const int first = a.req_start[req], last = a.req_start[req + 1];
@@ -921,32 +952,55 @@ __global__ void __launch_bounds__(256) selective_scan_kernel(ScanArgs a) {
         s[i] = n < a.N ? S[n] : 0.f;
         An[i] = n < a.N ? a.A[(size_t)cc * a.N + n] : 0.f;
     }
-    const float bias = a.bdt[cc], dskip = a.Dskip[cc];
-    const float *wdt = a.Wdt + (size_t)cc * a.K;
-    for (int t = first; t < last; ++t) {
-        const float *low = a.low + (size_t)t * a.ld_low;
-        float d = 0.f;
-        for (int k = part; k < a.K; k += SS_LANES) d = fmaf(wdt[k], low[k], d);
-#pragma unroll
-        for (int o = SS_LANES / 2; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
-        const float dt = softplus_f(d + bias);
-        const float xv = a.x[(size_t)t * a.E + cc];
-        const float dx = dt * xv;
-        const float *Bt = low + a.K, *Ct = low + a.K + a.N;
-        float y = 0.f;
-#pragma unroll
-        for (int i = 0; i < NPER; ++i) {
-            const int n = part + SS_LANES * i;
-            if (n < a.N) {
-                s[i] = fmaf(expf(dt * An[i]), s[i], dx * Bt[n]);
-                y = fmaf(s[i], Ct[n], y);
+    const float dskip = a.Dskip[cc];
+    for (int t0 = first; t0 < last; t0 += SS_CHUNK) {
+        const int n_rows = min(SS_CHUNK, last - t0);
+        for (int idx = threadIdx.x; idx < n_rows * SS_CHANNELS; idx += 256) {
+            const int tt = idx / SS_CHANNELS, ch = min(c0 + idx % SS_CHANNELS, a.E - 1);
+            const size_t t = (size_t)(t0 + tt);
+            float dt;
+            if (a.dt != nullptr) {
+                dt = a.dt[t * a.ld_dt + ch];
+            } else {
+                const float *low = a.low + t * a.ld_low, *w = a.Wdt + (size_t)ch * a.K;
+                float d = 0.f;
+                for (int k = 0; k < a.K; ++k) d = fmaf(w[k], low[k], d);
+                dt = softplus_f(d + a.bdt[ch]);
             }
+            s_dt[idx] = dt;
+            s_x[idx] = a.x[t * a.E + ch];
         }
+        for (int idx = threadIdx.x; idx < n_rows * a.N; idx += 256) {
+            const int tt = idx / a.N, n = idx % a.N;
+            const float *low = a.low + (size_t)(t0 + tt) * a.ld_low + a.K;
+            s_B[idx] = low[n];
+            s_C[idx] = low[a.N + n];
+        }
+        __syncthreads();
+        for (int tt = 0; tt < n_rows; ++tt) {
+            const float dt = s_dt[tt * SS_CHANNELS + cl], xv = s_x[tt * SS_CHANNELS + cl];
+            const float dx = dt * xv;
+            const float *Bt = s_B + tt * a.N, *Ct = s_C + tt * a.N;
+            float y = 0.f;
 #pragma unroll
-        for (int o = SS_LANES / 2; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
-        if (live && part == 0) {
-            y = fmaf(dskip, xv, y);
-            ((T *)a.out)[(size_t)t * a.E + c] = from_f32<T>(y * silu_f(a.z[(size_t)t * a.ld_z + c]));
+            for (int i = 0; i < NPER; ++i) {
+                const int n = part + SS_LANES * i;
+                if (n < a.N) {
+                    s[i] = fmaf(expf(dt * An[i]), s[i], dx * Bt[n]);
+                    y = fmaf(s[i], Ct[n], y);
+                }
+            }
+#pragma unroll
+            for (int o = SS_LANES / 2; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
+            if (part == 0) s_y[tt * SS_CHANNELS + cl] = fmaf(dskip, xv, y);
+        }
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < n_rows * SS_CHANNELS; idx += 256) {
+            const int tt = idx / SS_CHANNELS, ch = c0 + idx % SS_CHANNELS;
+            if (ch < a.E) {
+                const size_t t = (size_t)(t0 + tt);
+                ((T *)a.out)[t * a.E + ch] = from_f32<T>(s_y[idx] * silu_f(a.z[t * a.ld_z + ch]));
+            }
         }
     }
     if (live) {
@@ -958,18 +1012,30 @@ __global__ void __launch_bounds__(256) selective_scan_kernel(ScanArgs a) {
     }
 }
 
+// `dt_buf` (may be null): room for step sizes [T, ld_dt] that a step of many rows makes ahead with one product.
 JK_EXPORT int jk_selective_scan(const float *x, const float *low, int ld_low, int K, int N, int E, const float *z, int ld_z,
                                 const float *Wdt, const float *bdt, const float *A, const float *Dskip, float *state,
-                                const int *req_start, const int *slot_ids, int nreq, void *out, int dtype, cudaStream_t stream) {
+                                const int *req_start, const int *slot_ids, int nreq, void *out, int dtype, float *dt_buf, int ld_dt,
+                                int T, cudaStream_t stream) {
     if (nreq == 0) return JK_OK;
     JK_REQUIRE(x && low && z && Wdt && bdt && A && Dskip && state && req_start && slot_ids && out, "selective_scan: an argument is missing");
     JK_REQUIRE(K > 0 && N > 0 && E > 0 && ld_low >= K + 2 * N, "selective_scan: rank %d, states %d, channels %d, rows of %d", K, N, E, ld_low);
     JK_REQUIRE(N <= SS_LANES * 32, "selective_scan: %d states exceed %d", N, SS_LANES * 32);
     JK_REQUIRE(nreq <= 65535, "selective_scan: %d requests exceed one launch", nreq);
-    ScanArgs a{x, low, ld_low, K, N, E, z, ld_z, Wdt, bdt, A, Dskip, state, req_start, slot_ids, out};
-    dim3 grid((E + 256 / SS_LANES - 1) / (256 / SS_LANES), nreq);
+    const bool ahead = dt_buf != nullptr && T > 64;
+    if (ahead) {
+        jk_launch(scan_steps_kernel, dim3((T + GT_M - 1) / GT_M, (E + GT_N - 1) / GT_N), dim3(256), 0, stream, low, ld_low, Wdt, bdt, dt_buf, ld_dt, T, E, K);
+        JK_CHECK_LAUNCH("scan_steps");
+    }
+    ScanArgs a{x, low, ld_low, K, N, E, z, ld_z, Wdt, bdt, A, Dskip, state, req_start, slot_ids, out, ahead ? dt_buf : nullptr, ld_dt};
+    dim3 grid((E + SS_CHANNELS - 1) / SS_CHANNELS, nreq);
     const int per = (N + SS_LANES - 1) / SS_LANES;
-#define LAUNCH_N(TT, NPER) jk_launch(selective_scan_kernel<TT, NPER>, grid, dim3(256), 0, stream, a)
+    const size_t smem = (size_t)SS_CHUNK * (3 * SS_CHANNELS + 2 * N) * sizeof(float);
+#define LAUNCH_N(TT, NPER)                                                                                                                  \
+    do {                                                                                                                                    \
+        if (smem > 48 * 1024) cudaFuncSetAttribute(selective_scan_kernel<TT, NPER>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        jk_launch(selective_scan_kernel<TT, NPER>, grid, dim3(256), smem, stream, a);                                                       \
+    } while (0)
 #define LAUNCH(TT)                              \
     if (per <= 1) LAUNCH_N(TT, 1);              \
     else if (per <= 2) LAUNCH_N(TT, 2);         \

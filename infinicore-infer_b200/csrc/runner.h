@@ -70,7 +70,8 @@ typedef long long (*LatentScratchFn)(int, int, int, int);
 typedef int (*CausalConvFn)(const float *, int, int, int, const float *, const float *, int, int, float *, const int *, const int *,
                             const int *, float *, void *, int, int, int, cudaStream_t);
 typedef int (*SelectiveScanFn)(const float *, const float *, int, int, int, int, const float *, int, const float *, const float *,
-                               const float *, const float *, float *, const int *, const int *, int, void *, int, cudaStream_t);
+                               const float *, const float *, float *, const int *, const int *, int, void *, int, float *, int, int,
+                               cudaStream_t);
 typedef int (*RoutedExpertsFn)(const void *, const float *, const void *, const void *, float *, int, int, int, int, int, int, int, int,
                                int *, void *, float *, cudaStream_t);
 typedef long long (*RoutedWorkspaceFn)(int, int, int);
@@ -185,7 +186,8 @@ enum RunnerOpKind {
     OP_LATENT_ATTENTION,// out[t, h] = softmax(q[t, h] . page rows * scale, causal) (page rows' first `rank` elements)
     OP_CAUSAL_CONV,     // in: float32 rows; n channels at q_off pass `taps` taps over time (+ bias, act); out = activations,
                         // out2 = float32; the request's tails (state) move forward
-    OP_SELECTIVE_SCAN,  // in = x [T, n] float32, in2 = [dt part (rank) | B (k) | C (k)] float32, z = SLOT_TMP[t, g_off + c];
+    OP_SELECTIVE_SCAN,  // in = x [T, n] float32, in2 = [dt part (rank) | B (k) | C (k)] float32, z = SLOT_TMP[t, g_off + c]; the n
+                        // columns of SLOT_TMP at q_off (the in-projection's x part, dead by now) take the step sizes of long steps;
                         // S = exp(dt A) S + dt x B, y = S C + D x over each request's rows and its state slot; out = y silu(z)
     OP_EXPERTS,         // SLOT_DELTA (+)= sum over each row's `top` experts of largest sigmoid(vec in) of expert(score * in)
     OP_SOFTCAP,         // logits = cap * tanh(logits / cap) over the wanted rows

@@ -715,15 +715,17 @@ def causal_conv(u: torch.Tensor, off: int, channels: int, taps: torch.Tensor, bi
 
 
 def selective_scan(x: torch.Tensor, low: torch.Tensor, dt_rank: int, states: int, z: torch.Tensor, z_ld: int, w_dt, dt_bias, A, skip,
-                   state: torch.Tensor, req_start, slot_ids, out: torch.Tensor) -> torch.Tensor:
-    """The selective scan of csrc/blocks.cu over each request's rows, from and into ``state [slots, channels, states]``."""
+                   state: torch.Tensor, req_start, slot_ids, out: torch.Tensor, dt_buf: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The selective scan of csrc/blocks.cu over each request's rows, from and into ``state [slots, channels, states]``.
+    ``dt_buf`` (float32 ``[T, channels]``): room in which a step of more than 64 rows makes its step sizes ahead."""
     for t, n in ((x, "x"), (low, "low"), (w_dt, "w_dt"), (dt_bias, "dt_bias"), (A, "A"), (skip, "skip"), (state, "state")):
         _need(t, n, torch.float32)
     _need(z, "z", torch.float32, contiguous=False)
     lib = _build.load("blocks")
     _check("blocks", lib.jk_selective_scan(_ptr(x), _ptr(low), _c_int(low.shape[1]), _c_int(dt_rank), _c_int(states), _c_int(x.shape[1]),
                                            _ptr(z), _c_int(z_ld), _ptr(w_dt), _ptr(dt_bias), _ptr(A), _ptr(skip), _ptr(state), _ptr(req_start),
-                                           _ptr(slot_ids), _c_int(req_start.numel() - 1), _ptr(out), _c_int(dtype_code(out.dtype)), _stream()))
+                                           _ptr(slot_ids), _c_int(req_start.numel() - 1), _ptr(out), _c_int(dtype_code(out.dtype)), _ptr(dt_buf),
+                                           _c_int(dt_buf.shape[1] if dt_buf is not None else 0), _c_int(x.shape[0]), _stream()))
     return out
 
 

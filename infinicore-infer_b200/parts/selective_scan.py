@@ -72,7 +72,7 @@ class SelectiveScan:
                    bias=self.conv_bias, act=ACT["silu"], state=tails),
             record("linear", "o", "scan", n=K + 2 * N, k=E, w=self.w_x),
             record("selective_scan", "mix", "act", in2_slot="scan", n=E, k=N, rank=K, w2=self.w_dt, b2=self.dt_bias, decay=self.A,
-                   vec=self.skip, g_off=E, ld=2 * E, state=view.state),
+                   vec=self.skip, q_off=0, g_off=E, ld=2 * E, state=view.state),
             record("linear", "act", "delta", n=s.hidden_size, k=E, w=self.w_o),
         ], keep=(self.w_in, self.w_x, self.w_o, self.taps, self.conv_bias, self.w_dt, self.dt_bias, self.skip, self.A, tails, view.state))
 

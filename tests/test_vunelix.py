@@ -380,7 +380,7 @@ def test_convolution_and_scan_carry_their_state_across_cuts_and_slots(E, N, K_, 
         low = (x32.double().cpu() @ w_x.T).float().to(dev)          # the small projection, here on the host
         out = torch.empty(2 * n, E, dtype=torch.float32, device=dev)
         K.selective_scan(x32, low, K_, N, rows[:, E:], ld, w_dt.float().to(dev), b_dt.float().to(dev), A, skip.float().to(dev), state,
-                         req_start, slots, out)
+                         req_start, slots, out, dt_buf=torch.empty(2 * n, E, dtype=torch.float32, device=dev) if a % 2 else None)
         got[0].append(out[:n].cpu()); got[1].append(out[n:].cpu())
     for i in range(2):
         err = (torch.cat(got[i]).double() - want[i]).abs().max().item() / want[i].abs().max().item()
