@@ -368,6 +368,55 @@ __device__ __forceinline__ void tile_product(const __nv_bfloat16 *__restrict__ A
     }
 }
 
+// C = A W^T for a float32 A and a bfloat16 W on the tensor cores without rounding A: every element of A is cut into two
+// bfloat16 halves (a = hi + lo, which keeps 16 bits of its mantissa) and both halves meet the same weights.
+__device__ __forceinline__ void tile_product_split(const float *__restrict__ A, size_t lda, int M, const __nv_bfloat16 *__restrict__ W, size_t ldw,
+                                                   int N, int K, int m0, int n0, float (&acc)[16]) {
+    __shared__ __align__(16) __nv_bfloat16 Ah[GT_M * TC_LD];
+    __shared__ __align__(16) __nv_bfloat16 Al[GT_M * TC_LD];
+    __shared__ __align__(16) __nv_bfloat16 Ws[GT_N * TC_LD];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int lr = tid / 4, lk = (tid % 4) * 8;
+    const int am = m0 + lr, wn = n0 + lr;
+    const float *arow = am < M ? A + (size_t)am * lda : nullptr;
+    const __nv_bfloat16 *wrow = wn < N ? W + (size_t)wn * ldw : nullptr;
+    const bool vec_w = ldw % 8 == 0 && (uintptr_t)W % 16 == 0;
+#pragma unroll
+    for (int e = 0; e < 16; ++e) acc[e] = 0.f;
+    const int a_row = (warp & 3) * 16 + (lane & 15), a_col = (lane >> 4) * 8;
+    const int b_row = (warp >> 2) * 32 + (lane >> 4) * 8 + (lane & 7), b_col = ((lane >> 3) & 1) * 8;
+    for (int k0 = 0; k0 < K; k0 += TC_K) {
+        __nv_bfloat16 h8[8], l8[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int k = k0 + lk + i;
+            const float v = (arow && k < K) ? arow[k] : 0.f;
+            h8[i] = __float2bfloat16_rn(v);
+            l8[i] = __float2bfloat16_rn(v - __bfloat162float(h8[i]));
+        }
+        *reinterpret_cast<uint4 *>(Ah + lr * TC_LD + lk) = *reinterpret_cast<const uint4 *>(h8);
+        *reinterpret_cast<uint4 *>(Al + lr * TC_LD + lk) = *reinterpret_cast<const uint4 *>(l8);
+        *reinterpret_cast<uint4 *>(Ws + lr * TC_LD + lk) = fetch8(wrow, k0 + lk, K, vec_w);
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < TC_K; kk += 16) {
+            unsigned h0, h1, h2, h3, l0, l1, l2, l3;
+            ldmatrix_x4(h0, h1, h2, h3, Ah + a_row * TC_LD + kk + a_col);
+            ldmatrix_x4(l0, l1, l2, l3, Al + a_row * TC_LD + kk + a_col);
+#pragma unroll
+            for (int p = 0; p < 2; ++p) {
+                unsigned b0, b1, b2, b3;
+                ldmatrix_x4(b0, b1, b2, b3, Ws + (b_row + p * 16) * TC_LD + kk + b_col);
+                mma_bf16_16816(acc + (2 * p) * 4, l0, l1, l2, l3, b0, b1);
+                mma_bf16_16816(acc + (2 * p + 1) * 4, l0, l1, l2, l3, b2, b3);
+                mma_bf16_16816(acc + (2 * p) * 4, h0, h1, h2, h3, b0, b1);
+                mma_bf16_16816(acc + (2 * p + 1) * 4, h0, h1, h2, h3, b2, b3);
+            }
+        }
+        __syncthreads();
+    }
+}
+
 // out[t, h * out_hs + n] = T(sum_k in[t, h * K + k] * w[h, n, k]) (* sigmoid(gate[t * gate_ld + h * N + n]))
 template <typename T>
 __global__ void __launch_bounds__(256) head_linear_kernel(const T *__restrict__ in, const T *__restrict__ w, T *__restrict__ out, int rows, int H,
@@ -542,7 +591,8 @@ __global__ void latent_merge_kernel(const float *__restrict__ part, T *__restric
 // has pairs mw * 16 .. + 15; for the scores it takes the tile's keys nw * 8 .. + 7 over the whole row width, the four nw
 // warps exchange scores through shared memory, every thread forms the softmax weights of its own fragment (float32; the
 // maximum and the sum go around the four lanes that share a row), and for the weighted sum it owns the output columns
-// nw * NT * 8 .. of all 32 keys, the cached tile serving as the value operand through ldmatrix.trans.  Ranges as above.
+// nw * NT * 8 .. of all 32 keys, the cached tile serving as the value operand through ldmatrix.trans.  Tiles of cached
+// rows arrive by asynchronous copies into two buffers that take turns.  Ranges as above.
 constexpr int LT_PAIRS = 32, LT_KEYS = 32;
 
 struct LatentTcArgs {
@@ -591,14 +641,28 @@ __global__ void __launch_bounds__(256) latent_attention_tc_kernel(LatentTcArgs a
     const int h0 = blockIdx.y * a.HT;
     const int D = a.R + a.dr, DP = (D + 15) / 16 * 16, LDK = a.ldk, LDQ = DP + 8;
     __nv_bfloat16 *Qs = reinterpret_cast<__nv_bfloat16 *>(lt_smem);                 // [32][LDQ]
-    __nv_bfloat16 *Ks = Qs + LT_PAIRS * LDQ;                                        // [32][LDK]
-    float *Sb = reinterpret_cast<float *>(Ks + LT_KEYS * LDK);                      // [2][16][33]
+    __nv_bfloat16 *Kbuf = Qs + LT_PAIRS * LDQ;                                      // two tiles of [32][LDK] that take turns
+    float *Sb = reinterpret_cast<float *>(Kbuf + 2 * LT_KEYS * LDK);                // [2][16][33]
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, mw = warp & 1, nw = warp >> 1;
-    for (int idx = tid; idx < LT_PAIRS * LDQ; idx += 256) {
-        const int p = idx / LDQ, e = idx % LDQ, r = p / a.HT, h = h0 + p % a.HT;
-        float v = 0.f;
-        if (r < nrows && h < a.H && e < D) v = __bfloat162float(a.q[((size_t)(t0 + r) * a.H + h) * D + e]);
-        Qs[idx] = __float2bfloat16_rn(v);
+    const bool vec = D % 8 == 0 && (uintptr_t)a.pages % 16 == 0 && (uintptr_t)a.q % 16 == 0;
+    {
+        const int q8 = LDQ / 8;
+        for (int idx = tid; idx < LT_PAIRS * q8; idx += 256) {
+            const int p = idx / q8, e = (idx % q8) * 8, r = p / a.HT, h = h0 + p % a.HT;
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (r < nrows && h < a.H && e < D) {
+                const __nv_bfloat16 *src = a.q + ((size_t)(t0 + r) * a.H + h) * D + e;
+                if (vec && e + 8 <= D) {
+                    v = *reinterpret_cast<const uint4 *>(src);
+                } else {
+                    __nv_bfloat16 tmp[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) tmp[i] = e + i < D ? src[i] : __float2bfloat16_rn(0.f);
+                    v = *reinterpret_cast<const uint4 *>(tmp);
+                }
+            }
+            *reinterpret_cast<uint4 *>(Qs + p * LDQ + e) = v;
+        }
     }
     const int max_pos = a.positions[t0 + nrows - 1];
     int lo = 0, hi = max_pos + 1;
@@ -617,26 +681,41 @@ __global__ void __launch_bounds__(256) latent_attention_tc_kernel(LatentTcArgs a
 #pragma unroll
     for (int i = 0; i < NT; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
     const int *bt = a.block_table + (size_t)req * a.max_blocks;
-    const bool vec = D % 8 == 0 && (uintptr_t)a.pages % 16 == 0;
     const int c8n = LDK / 8;
-    for (int j0 = lo; j0 < hi; j0 += LT_KEYS) {
+    // A tile of cached rows into one of the two buffers: 16-byte asynchronous copies (zeros where there is no row or no
+    // column) when rows are multiples of 16 bytes, else element by element.  The tile after the one at work is always
+    // on its way.
+    auto fetch_tile = [&](int j0, __nv_bfloat16 *Ks) {
         const int n = min(LT_KEYS, hi - j0);
         for (int idx = tid; idx < LT_KEYS * c8n; idx += 256) {
             const int r = idx / c8n, c = (idx % c8n) * 8;
-            uint4 v = make_uint4(0u, 0u, 0u, 0u);
-            if (r < n && c < D) {
-                const int j = j0 + r;
-                const __nv_bfloat16 *src = a.pages + ((size_t)bt[j / a.page_size] * a.page_size + (size_t)(j % a.page_size)) * D + c;
-                if (vec && c + 8 <= D) {
-                    v = *reinterpret_cast<const uint4 *>(src);
-                } else {
-                    __nv_bfloat16 tmp[8];
+            const bool there = r < n && c < D;
+            const int j = there ? j0 + r : lo;
+            const __nv_bfloat16 *src = a.pages + ((size_t)bt[j / a.page_size] * a.page_size + (size_t)(j % a.page_size)) * D + (there ? c : 0);
+            __nv_bfloat16 *dst = Ks + r * LDK + c;
+            if (vec) {
+                const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+                const int bytes = there ? 16 : 0;
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(src), "r"(bytes) : "memory");
+            } else {
+                __nv_bfloat16 tmp[8];
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) tmp[i] = c + i < D ? src[i] : __float2bfloat16_rn(0.f);
-                    v = *reinterpret_cast<const uint4 *>(tmp);
-                }
+                for (int i = 0; i < 8; ++i) tmp[i] = (there && c + i < D) ? src[i] : __float2bfloat16_rn(0.f);
+                *reinterpret_cast<uint4 *>(dst) = *reinterpret_cast<const uint4 *>(tmp);
             }
-            *reinterpret_cast<uint4 *>(Ks + r * LDK + c) = v;
+        }
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
+    };
+    if (lo < hi) fetch_tile(lo, Kbuf);
+    int turn = 0;
+    for (int j0 = lo; j0 < hi; j0 += LT_KEYS, turn ^= 1) {
+        const int n = min(LT_KEYS, hi - j0);
+        const __nv_bfloat16 *Ks = Kbuf + turn * LT_KEYS * LDK;
+        if (j0 + LT_KEYS < hi) {
+            fetch_tile(j0 + LT_KEYS, Kbuf + (turn ^ 1) * LT_KEYS * LDK);
+            asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;\n" ::: "memory");
         }
         __syncthreads();
         // scores of this warp's pairs against the keys nw * 8 .. + 7
@@ -764,7 +843,7 @@ JK_EXPORT int jk_latent_attention(const void *q, const void *pages, void *out, f
         const int DP = (D + 15) / 16 * 16, ldk = std::max(DP, 4 * NT * 8) + 8;
         LatentTcArgs ta{(const __nv_bfloat16 *)q, (const __nv_bfloat16 *)pages, (__nv_bfloat16 *)out, part, positions, req_start, block_table,
                         nreq, H, R, dr, page_size, max_blocks, splits, HT, RT, ldk, scale};
-        const size_t smem_tc = (size_t)LT_PAIRS * (DP + 8) * 2 + (size_t)LT_KEYS * ldk * 2 + 2 * 16 * 33 * sizeof(float);
+        const size_t smem_tc = (size_t)LT_PAIRS * (DP + 8) * 2 + 2 * (size_t)LT_KEYS * ldk * 2 + 2 * 16 * 33 * sizeof(float);
         dim3 grid((T + RT - 1) / RT + nreq, (H + HT - 1) / HT, splits);
         JK_REQUIRE(grid.y <= 65535, "latent_attention: %d heads", H);
 #define LAUNCH_TC(NT_)                                                                                                                       \
@@ -904,7 +983,8 @@ struct ScanArgs {
     int ld_low, K, N, E;
     const float *z;         // z_t[c] = z[t * ld_z + c]
     int ld_z;
-    const float *Wdt, *bdt, *A, *Dskip;
+    const void *Wdt;        // [E, K] in the activation type (float32 mode: float; bfloat16 mode: as the checkpoint stores it)
+    const float *bdt, *A, *Dskip;
     float *state;
     const int *req_start, *slot_ids;
     void *out;
@@ -912,18 +992,26 @@ struct ScanArgs {
     int ld_dt;
 };
 
-// dt[t, c] = softplus(low[t, :K] . Wdt[c] + bdt[c]) for a step of many rows: a float32 product on the CUDA cores
-__global__ void __launch_bounds__(256) scan_steps_kernel(const float *__restrict__ low, int ld_low, const float *__restrict__ Wdt,
+// dt[t, c] = softplus(low[t, :K] . Wdt[c] + bdt[c]) ahead of the scan, as one product: float32 weights on the CUDA
+// cores; bfloat16 weights (as a 16-bit checkpoint stores them) on the tensor cores with the float32 rows cut in two
+// halves, so that nothing of them is rounded away.  The sums and the softplus are float32.
+template <typename TW>
+__global__ void __launch_bounds__(256) scan_steps_kernel(const float *__restrict__ low, int ld_low, const TW *__restrict__ Wdt,
                                                          const float *__restrict__ bdt, float *__restrict__ dt, int ld_dt, int rows, int E, int K) {
     pdl_trigger();
     pdl_wait();
     const int m0 = blockIdx.x * GT_M, n0 = blockIdx.y * GT_N;
-    float acc[16], unused[16];
-    tile_product<false>(low, (size_t)ld_low, nullptr, rows, Wdt, (const float *)nullptr, (size_t)K, E, K, m0, n0, acc, unused);
+    float acc[16];
+    if constexpr (OnTensorCores<TW>::value) {
+        tile_product_split(low, (size_t)ld_low, rows, Wdt, (size_t)K, E, K, m0, n0, acc);
+    } else {
+        float unused[16];
+        tile_product<false>(low, (size_t)ld_low, nullptr, rows, Wdt, (const float *)nullptr, (size_t)K, E, K, m0, n0, acc, unused);
+    }
 #pragma unroll
     for (int e = 0; e < 16; ++e) {
         int r, c;
-        tile_at<float>(e, &r, &c);
+        tile_at<TW>(e, &r, &c);
         const int t = m0 + r, ch = n0 + c;
         if (t < rows && ch < E) dt[(size_t)t * ld_dt + ch] = softplus_f(acc[e] + bdt[ch]);
     }
@@ -962,9 +1050,10 @@ __global__ void __launch_bounds__(256) selective_scan_kernel(ScanArgs a) {
             if (a.dt != nullptr) {
                 dt = a.dt[t * a.ld_dt + ch];
             } else {
-                const float *low = a.low + t * a.ld_low, *w = a.Wdt + (size_t)ch * a.K;
+                const float *low = a.low + t * a.ld_low;
+                const T *w = (const T *)a.Wdt + (size_t)ch * a.K;
                 float d = 0.f;
-                for (int k = 0; k < a.K; ++k) d = fmaf(w[k], low[k], d);
+                for (int k = 0; k < a.K; ++k) d = fmaf(to_f32(w[k]), low[k], d);
                 dt = softplus_f(d + a.bdt[ch]);
             }
             s_dt[idx] = dt;
@@ -1012,9 +1101,10 @@ __global__ void __launch_bounds__(256) selective_scan_kernel(ScanArgs a) {
     }
 }
 
-// `dt_buf` (may be null): room for step sizes [T, ld_dt] that a step of many rows makes ahead with one product.
+// `dt_buf` (may be null): room for step sizes [T, ld_dt], made ahead with one product; without it they are formed while
+// the rows are staged.  `Wdt` is of the type `dtype` names.
 JK_EXPORT int jk_selective_scan(const float *x, const float *low, int ld_low, int K, int N, int E, const float *z, int ld_z,
-                                const float *Wdt, const float *bdt, const float *A, const float *Dskip, float *state,
+                                const void *Wdt, const float *bdt, const float *A, const float *Dskip, float *state,
                                 const int *req_start, const int *slot_ids, int nreq, void *out, int dtype, float *dt_buf, int ld_dt,
                                 int T, cudaStream_t stream) {
     if (nreq == 0) return JK_OK;
@@ -1022,9 +1112,12 @@ JK_EXPORT int jk_selective_scan(const float *x, const float *low, int ld_low, in
     JK_REQUIRE(K > 0 && N > 0 && E > 0 && ld_low >= K + 2 * N, "selective_scan: rank %d, states %d, channels %d, rows of %d", K, N, E, ld_low);
     JK_REQUIRE(N <= SS_LANES * 32, "selective_scan: %d states exceed %d", N, SS_LANES * 32);
     JK_REQUIRE(nreq <= 65535, "selective_scan: %d requests exceed one launch", nreq);
-    const bool ahead = dt_buf != nullptr && T > 64;
+    const bool ahead = dt_buf != nullptr;
     if (ahead) {
-        jk_launch(scan_steps_kernel, dim3((T + GT_M - 1) / GT_M, (E + GT_N - 1) / GT_N), dim3(256), 0, stream, low, ld_low, Wdt, bdt, dt_buf, ld_dt, T, E, K);
+        const dim3 tiles((T + GT_M - 1) / GT_M, (E + GT_N - 1) / GT_N);
+#define LAUNCH(TT) jk_launch(scan_steps_kernel<TT>, tiles, dim3(256), 0, stream, low, ld_low, (const TT *)Wdt, bdt, dt_buf, ld_dt, T, E, K)
+        BLOCKS_BY_DTYPE(dtype, "scan_steps", LAUNCH);
+#undef LAUNCH
         JK_CHECK_LAUNCH("scan_steps");
     }
     ScanArgs a{x, low, ld_low, K, N, E, z, ld_z, Wdt, bdt, A, Dskip, state, req_start, slot_ids, out, ahead ? dt_buf : nullptr, ld_dt};

@@ -69,7 +69,7 @@ typedef int (*LatentAttentionFn)(const void *, const void *, void *, float *, in
 typedef long long (*LatentScratchFn)(int, int, int, int);
 typedef int (*CausalConvFn)(const float *, int, int, int, const float *, const float *, int, int, float *, const int *, const int *,
                             const int *, float *, void *, int, int, int, cudaStream_t);
-typedef int (*SelectiveScanFn)(const float *, const float *, int, int, int, int, const float *, int, const float *, const float *,
+typedef int (*SelectiveScanFn)(const float *, const float *, int, int, int, int, const float *, int, const void *, const float *,
                                const float *, const float *, float *, const int *, const int *, int, void *, int, float *, int, int,
                                cudaStream_t);
 typedef int (*RoutedExpertsFn)(const void *, const float *, const void *, const void *, float *, int, int, int, int, int, int, int, int,
@@ -249,7 +249,7 @@ struct RunnerOp {
     // NORM_ADD: vec = the norm's weight.  REINJECT: vec = the row added to every row.  LATENT_QKV: heads, head_dim (plain
     // part), rank (latent size), rot_dims, freq, norm_k (the latent norm's weight), eps, q_off, k_off (the latent's column).
     // CAUSAL_CONV: conv_q = taps [n, taps], bias, act, state = tails [slots, taps - 1, n].  SELECTIVE_SCAN: n channels, k
-    // states, w2 = the step size's projection [n, rank] (float32), b2 its bias, decay = A [n, k], vec = D, state [slots, n, k].
+    // states, w2 = the step size's projection [n, rank] (compute type), b2 its bias, decay = A [n, k], vec = D, state [slots, n, k].
     // EXPERTS: n = hidden, vec = the router [experts, hidden] (float32), act = the experts' activation.
 };
 

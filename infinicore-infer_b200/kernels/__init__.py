@@ -717,9 +717,10 @@ def causal_conv(u: torch.Tensor, off: int, channels: int, taps: torch.Tensor, bi
 def selective_scan(x: torch.Tensor, low: torch.Tensor, dt_rank: int, states: int, z: torch.Tensor, z_ld: int, w_dt, dt_bias, A, skip,
                    state: torch.Tensor, req_start, slot_ids, out: torch.Tensor, dt_buf: Optional[torch.Tensor] = None) -> torch.Tensor:
     """The selective scan of csrc/blocks.cu over each request's rows, from and into ``state [slots, channels, states]``.
-    ``dt_buf`` (float32 ``[T, channels]``): room in which a step of more than 64 rows makes its step sizes ahead."""
-    for t, n in ((x, "x"), (low, "low"), (w_dt, "w_dt"), (dt_bias, "dt_bias"), (A, "A"), (skip, "skip"), (state, "state")):
+    ``w_dt`` is of ``out``'s type.  ``dt_buf`` (float32 ``[T, channels]``): room in which the step sizes are made ahead."""
+    for t, n in ((x, "x"), (low, "low"), (dt_bias, "dt_bias"), (A, "A"), (skip, "skip"), (state, "state")):
         _need(t, n, torch.float32)
+    _need(w_dt, "w_dt", out.dtype)
     _need(z, "z", torch.float32, contiguous=False)
     lib = _build.load("blocks")
     _check("blocks", lib.jk_selective_scan(_ptr(x), _ptr(low), _c_int(low.shape[1]), _c_int(dt_rank), _c_int(states), _c_int(x.shape[1]),

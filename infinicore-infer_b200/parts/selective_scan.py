@@ -30,7 +30,7 @@ class SelectiveScan:
                 spec.conv_name: TensorDecl((E, spec.conv_taps), VECTOR, init="taps"),
                 spec.conv_name + b: TensorDecl((E,), VECTOR, init="zeros"),
                 spec.x_name: TensorDecl((K + 2 * N, E)),
-                spec.dt_name: TensorDecl((E, K), VECTOR),
+                spec.dt_name: TensorDecl((E, K)),
                 spec.dt_name + b: TensorDecl((E,), VECTOR, init="zeros"),
                 spec.a_log_name: TensorDecl((E, N), VECTOR, init="zeros"),
                 spec.d_name: TensorDecl((E,), VECTOR, init="ones"),
@@ -53,7 +53,8 @@ class SelectiveScan:
         self.w_x = weights.get(prefix + spec.x_name, MATRIX)
         self.w_o = weights.get(prefix + spec.o_name, MATRIX)
         self.taps, self.conv_bias = vec(spec.conv_name), vec(spec.conv_name + b)
-        self.w_dt, self.dt_bias, self.skip = vec(spec.dt_name), vec(spec.dt_name + b), vec(spec.d_name)
+        self.w_dt = weights.get(prefix + spec.dt_name, MATRIX)      # float32 rows meet it unrounded (csrc/blocks.cu: scan_steps)
+        self.dt_bias, self.skip = vec(spec.dt_name + b), vec(spec.d_name)
         self.A = (-torch.exp(vec(spec.a_log_name).to(torch.float32))).contiguous()
 
     def weight_bytes(self) -> int:
