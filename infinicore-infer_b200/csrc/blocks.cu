@@ -602,6 +602,7 @@ struct LatentTcArgs {
     const int *positions, *req_start, *block_table;
     int nreq, H, R, dr, page_size, max_blocks, splits, HT, RT, ldk;
     float scale;
+    int buffers;        // 2: the tile after the one at work is on its way; 1: where two would leave an SM room for one block only
 };
 
 __device__ __forceinline__ void ldmatrix_x2(unsigned &r0, unsigned &r1, const void *smem_row) {
@@ -642,7 +643,7 @@ __global__ void __launch_bounds__(256) latent_attention_tc_kernel(LatentTcArgs a
     const int D = a.R + a.dr, DP = (D + 15) / 16 * 16, LDK = a.ldk, LDQ = DP + 8;
     __nv_bfloat16 *Qs = reinterpret_cast<__nv_bfloat16 *>(lt_smem);                 // [32][LDQ]
     __nv_bfloat16 *Kbuf = Qs + LT_PAIRS * LDQ;                                      // two tiles of [32][LDK] that take turns
-    float *Sb = reinterpret_cast<float *>(Kbuf + 2 * LT_KEYS * LDK);                // [2][16][33]
+    float *Sb = reinterpret_cast<float *>(Kbuf + a.buffers * LT_KEYS * LDK);        // [2][16][33]
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, mw = warp & 1, nw = warp >> 1;
     const bool vec = D % 8 == 0 && (uintptr_t)a.pages % 16 == 0 && (uintptr_t)a.q % 16 == 0;
     {
@@ -681,37 +682,47 @@ __global__ void __launch_bounds__(256) latent_attention_tc_kernel(LatentTcArgs a
 #pragma unroll
     for (int i = 0; i < NT; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
     const int *bt = a.block_table + (size_t)req * a.max_blocks;
-    const int c8n = LDK / 8;
     // A tile of cached rows into one of the two buffers: 16-byte asynchronous copies (zeros where there is no row or no
     // column) when rows are multiples of 16 bytes, else element by element.  The tile after the one at work is always
     // on its way.
     auto fetch_tile = [&](int j0, __nv_bfloat16 *Ks) {
         const int n = min(LT_KEYS, hi - j0);
-        for (int idx = tid; idx < LT_KEYS * c8n; idx += 256) {
-            const int r = idx / c8n, c = (idx % c8n) * 8;
-            const bool there = r < n && c < D;
-            const int j = there ? j0 + r : lo;
-            const __nv_bfloat16 *src = a.pages + ((size_t)bt[j / a.page_size] * a.page_size + (size_t)(j % a.page_size)) * D + (there ? c : 0);
-            __nv_bfloat16 *dst = Ks + r * LDK + c;
-            if (vec) {
-                const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
-                const int bytes = there ? 16 : 0;
-                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(src), "r"(bytes) : "memory");
-            } else {
-                __nv_bfloat16 tmp[8];
+        const __nv_bfloat16 *src_row[4];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) tmp[i] = (there && c + i < D) ? src[i] : __float2bfloat16_rn(0.f);
-                *reinterpret_cast<uint4 *>(dst) = *reinterpret_cast<const uint4 *>(tmp);
+        for (int i = 0; i < 4; ++i) {           // a warp brings rows warp, warp + 8, ...; their places first, then the copies
+            const int r = warp + 8 * i, j = r < n ? j0 + r : lo;
+            src_row[i] = a.pages + ((size_t)bt[j / a.page_size] * a.page_size + (size_t)(j % a.page_size)) * D;
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int r = warp + 8 * i;
+            __nv_bfloat16 *dst_row = Ks + r * LDK;
+            for (int c = lane * 8; c < LDK; c += 256) {
+                const bool there = r < n && c < D;
+                if (vec) {
+                    const unsigned d = (unsigned)__cvta_generic_to_shared(dst_row + c);
+                    const int bytes = there ? 16 : 0;
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(src_row[i] + (there ? c : 0)), "r"(bytes) : "memory");
+                } else {
+                    __nv_bfloat16 tmp[8];
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) tmp[e] = (there && c + e < D) ? src_row[i][c + e] : __float2bfloat16_rn(0.f);
+                    *reinterpret_cast<uint4 *>(dst_row + c) = *reinterpret_cast<const uint4 *>(tmp);
+                }
             }
         }
         asm volatile("cp.async.commit_group;\n" ::: "memory");
     };
-    if (lo < hi) fetch_tile(lo, Kbuf);
+    const bool two = a.buffers > 1;
+    if (lo < hi && two) fetch_tile(lo, Kbuf);
     int turn = 0;
-    for (int j0 = lo; j0 < hi; j0 += LT_KEYS, turn ^= 1) {
+    for (int j0 = lo; j0 < hi; j0 += LT_KEYS, turn ^= (two ? 1 : 0)) {
         const int n = min(LT_KEYS, hi - j0);
         const __nv_bfloat16 *Ks = Kbuf + turn * LT_KEYS * LDK;
-        if (j0 + LT_KEYS < hi) {
+        if (!two) {
+            fetch_tile(j0, Kbuf);
+            asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+        } else if (j0 + LT_KEYS < hi) {
             fetch_tile(j0 + LT_KEYS, Kbuf + (turn ^ 1) * LT_KEYS * LDK);
             asm volatile("cp.async.wait_group 1;\n" ::: "memory");
         } else {
@@ -719,12 +730,28 @@ __global__ void __launch_bounds__(256) latent_attention_tc_kernel(LatentTcArgs a
         }
         __syncthreads();
         // scores of this warp's pairs against the keys nw * 8 .. + 7
-        float s[4] = {0.f, 0.f, 0.f, 0.f};
-        for (int kk = 0; kk < DP; kk += 16) {
-            unsigned a0, a1, a2, a3, b0, b1;
-            ldmatrix_x4(a0, a1, a2, a3, Qs + (mw * 16 + (lane & 15)) * LDQ + kk + (lane >> 4) * 8);
-            ldmatrix_x2(b0, b1, Ks + (nw * 8 + (lane & 7)) * LDK + kk + ((lane >> 3) & 1) * 8);
-            mma_bf16_16816(s, a0, a1, a2, a3, b0, b1);
+        float s[4] = {0.f, 0.f, 0.f, 0.f}, s2[4] = {0.f, 0.f, 0.f, 0.f};      // two chains of sums that take turns
+        {
+            const __nv_bfloat16 *qp = Qs + (mw * 16 + (lane & 15)) * LDQ + (lane >> 4) * 8;
+            const __nv_bfloat16 *kp = Ks + (nw * 8 + (lane & 7)) * LDK + ((lane >> 3) & 1) * 8;
+            int kk = 0;
+            for (; kk + 32 <= DP; kk += 32) {
+                unsigned a0, a1, a2, a3, b0, b1, c0, c1, c2, c3, d0, d1;
+                ldmatrix_x4(a0, a1, a2, a3, qp + kk);
+                ldmatrix_x2(b0, b1, kp + kk);
+                ldmatrix_x4(c0, c1, c2, c3, qp + kk + 16);
+                ldmatrix_x2(d0, d1, kp + kk + 16);
+                mma_bf16_16816(s, a0, a1, a2, a3, b0, b1);
+                mma_bf16_16816(s2, c0, c1, c2, c3, d0, d1);
+            }
+            if (kk < DP) {
+                unsigned a0, a1, a2, a3, b0, b1;
+                ldmatrix_x4(a0, a1, a2, a3, qp + kk);
+                ldmatrix_x2(b0, b1, kp + kk);
+                mma_bf16_16816(s, a0, a1, a2, a3, b0, b1);
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) s[i] += s2[i];
         }
         {
             float *row_a = Sb + (mw * 16 + (lane >> 2)) * 33, *row_b = row_a + 8 * 33;
@@ -841,9 +868,12 @@ JK_EXPORT int jk_latent_attention(const void *q, const void *pages, void *out, f
         const int RT = LT_PAIRS / HT, tiles8 = (R + 7) / 8, per = (tiles8 + 3) / 4;
         const int NT = per <= 2 ? 2 : (per <= 4 ? 4 : (per <= 8 ? 8 : 16));
         const int DP = (D + 15) / 16 * 16, ldk = std::max(DP, 4 * NT * 8) + 8;
+        // two tile buffers unless that leaves an SM (about 227 KB, 1 KB a block reserved) room for one block where one buffer leaves room for two
+        const size_t fixed = (size_t)LT_PAIRS * (DP + 8) * 2 + 2 * 16 * 33 * sizeof(float), tile = (size_t)LT_KEYS * ldk * 2;
+        const int buffers = (fixed + 2 * tile > 112 * 1024 && fixed + tile <= 112 * 1024) ? 1 : 2;
         LatentTcArgs ta{(const __nv_bfloat16 *)q, (const __nv_bfloat16 *)pages, (__nv_bfloat16 *)out, part, positions, req_start, block_table,
-                        nreq, H, R, dr, page_size, max_blocks, splits, HT, RT, ldk, scale};
-        const size_t smem_tc = (size_t)LT_PAIRS * (DP + 8) * 2 + 2 * (size_t)LT_KEYS * ldk * 2 + 2 * 16 * 33 * sizeof(float);
+                        nreq, H, R, dr, page_size, max_blocks, splits, HT, RT, ldk, scale, buffers};
+        const size_t smem_tc = fixed + buffers * tile;
         dim3 grid((T + RT - 1) / RT + nreq, (H + HT - 1) / HT, splits);
         JK_REQUIRE(grid.y <= 65535, "latent_attention: %d heads", H);
 #define LAUNCH_TC(NT_)                                                                                                                       \
@@ -972,10 +1002,10 @@ JK_EXPORT int jk_causal_conv(const float *u, int ld, int off, int C, const float
 //     S[c, n] <- exp(dt_t[c] A[c, n]) S[c, n] + dt_t[c] x_t[c] B_t[n]
 //     y_t[c]   = sum_n S[c, n] C_t[n] + Dskip[c] x_t[c];   out_t[c] = T(y_t[c] * silu(z_t[c]))
 // all float32; S lives in state[slot, c, n] between steps.  Eight neighbouring lanes share a channel: lane `part` keeps
-// the states part, part + 8, ... in registers and a share of the K products; sums go around by shuffles.  A block of 256
-// threads owns 32 channels of one request and walks the request's rows.
+// the states part, part + 8, ... in registers.  A block of 128 threads owns 16 channels of one request and walks the
+// request's rows.
 // ---------------------------------------------------------------------------------------------------------------
-constexpr int SS_LANES = 8, SS_CHANNELS = 256 / SS_LANES, SS_CHUNK = 32;
+constexpr int SS_LANES = 8, SS_THREADS = 128, SS_CHANNELS = SS_THREADS / SS_LANES, SS_CHUNK = 32;
 
 struct ScanArgs {
     const float *x;         // [T, E] after convolution and activation
@@ -1018,14 +1048,15 @@ __global__ void __launch_bounds__(256) scan_steps_kernel(const float *__restrict
 }
 
 // Rows pass shared memory SS_CHUNK at a time (step sizes, inputs, B and C staged by all threads), so a row of the
-// recurrence costs no global load; a chunk's outputs leave together, times silu(z).
+// recurrence costs no global load and no exchange between lanes: a lane leaves its share of a row's sum in shared
+// memory, and a chunk's outputs are added up and leave together, times silu(z).
 template <typename T, int NPER>
-__global__ void __launch_bounds__(256) selective_scan_kernel(ScanArgs a) {
+__global__ void __launch_bounds__(SS_THREADS) selective_scan_kernel(ScanArgs a) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ float ss_smem[];
-    float *s_dt = ss_smem, *s_x = s_dt + SS_CHUNK * SS_CHANNELS, *s_y = s_x + SS_CHUNK * SS_CHANNELS;
-    float *s_B = s_y + SS_CHUNK * SS_CHANNELS, *s_C = s_B + SS_CHUNK * a.N;
+    float *s_dt = ss_smem, *s_x = s_dt + SS_CHUNK * SS_CHANNELS, *s_y = s_x + SS_CHUNK * SS_CHANNELS;      // s_y: [chunk][threads]
+    float *s_B = s_y + SS_CHUNK * SS_THREADS, *s_C = s_B + SS_CHUNK * a.N;
     const int req = blockIdx.y;
     const int part = threadIdx.x % SS_LANES, cl = threadIdx.x / SS_LANES;
     const int c0 = blockIdx.x * SS_CHANNELS, c = c0 + cl;
@@ -1040,10 +1071,9 @@ __global__ void __launch_bounds__(256) selective_scan_kernel(ScanArgs a) {
         s[i] = n < a.N ? S[n] : 0.f;
         An[i] = n < a.N ? a.A[(size_t)cc * a.N + n] : 0.f;
     }
-    const float dskip = a.Dskip[cc];
     for (int t0 = first; t0 < last; t0 += SS_CHUNK) {
         const int n_rows = min(SS_CHUNK, last - t0);
-        for (int idx = threadIdx.x; idx < n_rows * SS_CHANNELS; idx += 256) {
+        for (int idx = threadIdx.x; idx < n_rows * SS_CHANNELS; idx += SS_THREADS) {
             const int tt = idx / SS_CHANNELS, ch = min(c0 + idx % SS_CHANNELS, a.E - 1);
             const size_t t = (size_t)(t0 + tt);
             float dt;
@@ -1059,13 +1089,14 @@ __global__ void __launch_bounds__(256) selective_scan_kernel(ScanArgs a) {
             s_dt[idx] = dt;
             s_x[idx] = a.x[t * a.E + ch];
         }
-        for (int idx = threadIdx.x; idx < n_rows * a.N; idx += 256) {
+        for (int idx = threadIdx.x; idx < n_rows * a.N; idx += SS_THREADS) {
             const int tt = idx / a.N, n = idx % a.N;
             const float *low = a.low + (size_t)(t0 + tt) * a.ld_low + a.K;
             s_B[idx] = low[n];
             s_C[idx] = low[a.N + n];
         }
         __syncthreads();
+#pragma unroll 4
         for (int tt = 0; tt < n_rows; ++tt) {
             const float dt = s_dt[tt * SS_CHANNELS + cl], xv = s_x[tt * SS_CHANNELS + cl];
             const float dx = dt * xv;
@@ -1079,18 +1110,22 @@ __global__ void __launch_bounds__(256) selective_scan_kernel(ScanArgs a) {
                     y = fmaf(s[i], Ct[n], y);
                 }
             }
-#pragma unroll
-            for (int o = SS_LANES / 2; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
-            if (part == 0) s_y[tt * SS_CHANNELS + cl] = fmaf(dskip, xv, y);
+            s_y[tt * SS_THREADS + threadIdx.x] = y;
         }
         __syncthreads();
-        for (int idx = threadIdx.x; idx < n_rows * SS_CHANNELS; idx += 256) {
-            const int tt = idx / SS_CHANNELS, ch = c0 + idx % SS_CHANNELS;
+        for (int idx = threadIdx.x; idx < n_rows * SS_CHANNELS; idx += SS_THREADS) {
+            const int tt = idx / SS_CHANNELS, k = idx % SS_CHANNELS, ch = c0 + k;
             if (ch < a.E) {
                 const size_t t = (size_t)(t0 + tt);
-                ((T *)a.out)[t * a.E + ch] = from_f32<T>(s_y[idx] * silu_f(a.z[t * a.ld_z + ch]));
+                const float *share = s_y + tt * SS_THREADS + k * SS_LANES;
+                float y = 0.f;
+#pragma unroll
+                for (int i = 0; i < SS_LANES; ++i) y += share[i];
+                y = fmaf(a.Dskip[ch], s_x[idx], y);
+                ((T *)a.out)[t * a.E + ch] = from_f32<T>(y * silu_f(a.z[t * a.ld_z + ch]));
             }
         }
+        __syncthreads();        // the next chunk's rows overwrite what this pass still reads
     }
     if (live) {
 #pragma unroll
@@ -1123,11 +1158,11 @@ JK_EXPORT int jk_selective_scan(const float *x, const float *low, int ld_low, in
     ScanArgs a{x, low, ld_low, K, N, E, z, ld_z, Wdt, bdt, A, Dskip, state, req_start, slot_ids, out, ahead ? dt_buf : nullptr, ld_dt};
     dim3 grid((E + SS_CHANNELS - 1) / SS_CHANNELS, nreq);
     const int per = (N + SS_LANES - 1) / SS_LANES;
-    const size_t smem = (size_t)SS_CHUNK * (3 * SS_CHANNELS + 2 * N) * sizeof(float);
+    const size_t smem = (size_t)SS_CHUNK * (2 * SS_CHANNELS + SS_THREADS + 2 * N) * sizeof(float);
 #define LAUNCH_N(TT, NPER)                                                                                                                  \
     do {                                                                                                                                    \
         if (smem > 48 * 1024) cudaFuncSetAttribute(selective_scan_kernel<TT, NPER>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-        jk_launch(selective_scan_kernel<TT, NPER>, grid, dim3(256), smem, stream, a);                                                       \
+        jk_launch(selective_scan_kernel<TT, NPER>, grid, dim3(SS_THREADS), smem, stream, a);                                                \
     } while (0)
 #define LAUNCH(TT)                              \
     if (per <= 1) LAUNCH_N(TT, 1);              \
