@@ -51,4 +51,17 @@ PRESETS: Dict[str, Preset] = {
             {"type": "attention", "mixer": {"heads": 4, "kv_heads": 2, "dim": 24, "vdim": 24, "conv": 3, "rot": {"dims": 12, "base": 1e5},
                                             "scale": 0.2, "mask": {"size": 24}, "kv_from": 1}, "mlp": {"kind": "dense", "ff": 160}},
         ]), 0.1, 0.05, 16),
+    # a small Vunelix: a span of two layers that runs twice, latent attention, a selective scan, dense and routed feed-forwards
+    "vunelix-tiny": Preset(dict(
+        architecture="Vunelix", vocab=320, width=96, norm={"eps": 1e-5}, logit_softcap=25.0, loop={"start": 1, "stop": 3, "times": 2}, layers=[
+            {"type": "latent_attention", "mixer": {"heads": 4, "dim": 16, "rot_dim": 8, "vdim": 24, "kv_rank": 48, "scale": 0.2,
+                                                   "rot": {"base": 1e4, "dims": 8, "scaling": {"factor": 4.0, "original": 64, "fast": 16.0, "slow": 1.0}}},
+             "mlp": {"kind": "dense", "ff": 160}},
+            {"type": "mamba1", "mixer": {"inner": 128, "state": 12, "dt_rank": 6, "conv": 4},
+             "mlp": {"kind": "moe", "router": {"experts": 6, "top": 2}, "expert": {"ff": 48}, "shared": {"ff": 64}}},
+            {"type": "latent_attention", "mixer": {"heads": 2, "dim": 24, "rot_dim": 16, "vdim": 16, "kv_rank": 32, "scale": 0.15,
+                                                   "rot": {"base": 5e4, "dims": 12}}, "mlp": None},
+            {"type": "mamba1", "mixer": {"inner": 64, "state": 20, "dt_rank": 4, "conv": 3},
+             "mlp": {"kind": "moe", "router": {"experts": 4, "top": 1}, "expert": {"ff": 80}}},
+        ]), 0.1, 0.05, 16),
 }

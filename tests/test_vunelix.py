@@ -473,3 +473,31 @@ def test_greedy_generation_through_the_scheduler_matches_the_plain_model(folders
             best = int(row.argmax())
             assert tok == best or row[best] - row[tok] < 1e-4 * np.abs(row).max(), f"token {j} of a prompt of {len(p)}"
     eng.cache.check_invariants()
+
+
+def test_command_line_runs_a_small_model_with_random_weights(tmp_path):
+    """``--random vunelix-tiny`` with three prompts through the scheduler, greedy: the printed tokens are the plain model's."""
+    import re
+    import subprocess
+    import sys
+    from infinicore_infer_b200.config import PRESETS, VunelixConfig
+    from infinicore_infer_b200.weights import index_directory, read_tensor, write_model_folder
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    preset = PRESETS["vunelix-tiny"]
+    proc = subprocess.run([sys.executable, "-m", "infinicore_infer_b200.jiuge", "--nvidia", "--random", "vunelix-tiny", "--seed", "3",
+                           "--prompt-lens", "2,19,40", "--chunk-size", "11", "--num-pages", "24", "--max-batch", "3",
+                           "--max-tokens-per-step", "24", "--temperature", "0", "--max-steps", "8", "--dtype", "float32"],
+                          capture_output=True, text=True, cwd=root, timeout=900)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    got = {int(m.group(1)): [int(t) for t in m.group(2).split()] for m in re.finditer(r"request (\d+): ([\d ]*)", proc.stdout)}
+    assert sorted(got) == [0, 1, 2]
+    cfg = VunelixConfig.from_dict(preset.config)
+    write_model_folder(cfg, str(tmp_path), seed=3, std=preset.std, norm_std=preset.norm_std)
+    w = {n: read_tensor(i).float() for n, i in index_directory(str(tmp_path)).items()}
+    for k, n in enumerate((2, 19, 40)):
+        prompt = torch.randint(0, cfg.vocab, (n,), generator=torch.Generator().manual_seed(3 + k)).tolist()
+        assert len(got[k]) == 8
+        logits = plain.forward(prompt + got[k], cfg.to_dict(), w).numpy()
+        for j, tok in enumerate(got[k]):
+            row = logits[n + j - 1]
+            assert tok == int(row.argmax()) or row.max() - row[tok] < 1e-4 * np.abs(row).max(), f"request {k}, token {j}"
