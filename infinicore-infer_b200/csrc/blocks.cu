@@ -226,7 +226,7 @@ JK_EXPORT int jk_latent_qkv(const float *u, int ld, int q_off, int kv_off, int H
 // Tiled products: C[M, N] = A[M, K] W[N, K]^T with float32 accumulation, operands of type T.  A block of 256 threads
 // makes a tile of 64 x 64.  float operands: on the CUDA cores (FFMA in the order of K, a thread 4 x 4 of the tile, K
 // through shared memory 16 at a time).  bfloat16 operands: on the tensor cores (mma.sync m16n8k16, a warp 16 x 32 of the
-// tile, K through shared memory 32 at a time, fragments by ldmatrix).  Rows of A may be picked through an index (a_rows).
+// tile, K through shared memory 32 at a time by asynchronous copies three tiles deep, fragments by ldmatrix).  Rows of A may be picked through an index (a_rows).
 // With GLU a second weight tile W2 runs along and the epilogue sees both sums.  A thread holds 16 sums; tile_at() says
 // where sum e lies in the tile.  Used per head (head_linear) and per expert (expert products), where the problem depends
 // on the block.
@@ -316,13 +316,30 @@ __device__ __forceinline__ uint4 fetch8(const __nv_bfloat16 *row, int k, int K, 
     return v;
 }
 
+// eight elements of a row from k on into shared memory, zeros beyond K or where there is no row: an asynchronous 16-byte
+// copy where rows are 16-byte aligned, else element by element
+__device__ __forceinline__ void stage8(__nv_bfloat16 *dst, const __nv_bfloat16 *row, int k, int K, bool vec) {
+    if (vec) {
+        const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+        const int left = row != nullptr ? K - k : 0;
+        const int bytes = left >= 8 ? 16 : (left > 0 ? 2 * left : 0);
+        const __nv_bfloat16 *src = bytes > 0 ? row + k : dst;          // nothing is read when bytes is 0; the address only has to be one
+        if (bytes > 0) asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(src), "r"(bytes) : "memory");
+        else *reinterpret_cast<uint4 *>(dst) = make_uint4(0u, 0u, 0u, 0u);
+    } else {
+        *reinterpret_cast<uint4 *>(dst) = fetch8(row, k, K, false);
+    }
+}
+
+constexpr int TC_STAGES = 3;        // tiles of K in flight: a block keeps 2 x 5 KB (or 3 x with GLU) a stage on its way
+
 template <bool GLU>
 __device__ __forceinline__ void tile_product(const __nv_bfloat16 *__restrict__ A, size_t lda, const int *__restrict__ a_rows, int M,
                                              const __nv_bfloat16 *__restrict__ W, const __nv_bfloat16 *__restrict__ W2, size_t ldw, int N, int K,
                                              int m0, int n0, float (&acc)[16], float (&acc2)[16]) {
-    __shared__ __align__(16) __nv_bfloat16 As[GT_M * TC_LD];
-    __shared__ __align__(16) __nv_bfloat16 Ws[GT_N * TC_LD];
-    __shared__ __align__(16) __nv_bfloat16 W2s[GLU ? GT_N * TC_LD : 8];
+    __shared__ __align__(16) __nv_bfloat16 As[TC_STAGES][GT_M * TC_LD];
+    __shared__ __align__(16) __nv_bfloat16 Ws[TC_STAGES][GT_N * TC_LD];
+    __shared__ __align__(16) __nv_bfloat16 W2s[GLU ? TC_STAGES : 1][GLU ? GT_N * TC_LD : 8];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int lr = tid / 4, lk = (tid % 4) * 8;      // this thread stages row lr, k lk .. lk + 7 of each operand tile
     const int am = m0 + lr, wn = n0 + lr;
@@ -335,37 +352,43 @@ __device__ __forceinline__ void tile_product(const __nv_bfloat16 *__restrict__ A
     for (int e = 0; e < 16; ++e) { acc[e] = 0.f; acc2[e] = 0.f; }
     const int a_row = (warp & 3) * 16 + (lane & 15), a_col = (lane >> 4) * 8;
     const int b_row = (warp >> 2) * 32 + (lane >> 4) * 8 + (lane & 7), b_col = ((lane >> 3) & 1) * 8;
-    // the next tile's operands are asked for while this tile's products run
-    uint4 ra = fetch8(arow, lk, K, vec_a), rw = fetch8(wrow, lk, K, vec_w), rw2 = GLU ? fetch8(w2row, lk, K, vec_w) : make_uint4(0u, 0u, 0u, 0u);
-    for (int k0 = 0; k0 < K; k0 += TC_K) {
-        *reinterpret_cast<uint4 *>(As + lr * TC_LD + lk) = ra;
-        *reinterpret_cast<uint4 *>(Ws + lr * TC_LD + lk) = rw;
-        if (GLU) *reinterpret_cast<uint4 *>(W2s + lr * TC_LD + lk) = rw2;
-        __syncthreads();
-        if (k0 + TC_K < K) {
-            ra = fetch8(arow, k0 + TC_K + lk, K, vec_a);
-            rw = fetch8(wrow, k0 + TC_K + lk, K, vec_w);
-            if (GLU) rw2 = fetch8(w2row, k0 + TC_K + lk, K, vec_w);
+    const int nk = (K + TC_K - 1) / TC_K;
+    auto stage = [&](int kt) {          // tile kt of K into its buffer; a group is committed even when there is no such tile
+        if (kt < nk) {
+            const int b = kt % TC_STAGES, k = kt * TC_K + lk;
+            stage8(As[b] + lr * TC_LD + lk, arow, k, K, vec_a);
+            stage8(Ws[b] + lr * TC_LD + lk, wrow, k, K, vec_w);
+            if (GLU) stage8(W2s[b] + lr * TC_LD + lk, w2row, k, K, vec_w);
         }
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
+    };
+#pragma unroll
+    for (int i = 0; i < TC_STAGES - 1; ++i) stage(i);
+    for (int kt = 0; kt < nk; ++kt) {
+        asm volatile("cp.async.wait_group %0;\n" ::"n"(TC_STAGES - 2) : "memory");       // tile kt has landed (for this thread)
+        __syncthreads();                                                                  // ... and for all; the buffer of tile kt - 1 is free
+        stage(kt + TC_STAGES - 1);
+        const __nv_bfloat16 *as = As[kt % TC_STAGES], *ws = Ws[kt % TC_STAGES], *w2s = W2s[GLU ? kt % TC_STAGES : 0];
 #pragma unroll
         for (int kk = 0; kk < TC_K; kk += 16) {
             unsigned a0, a1, a2, a3;
-            ldmatrix_x4(a0, a1, a2, a3, As + a_row * TC_LD + kk + a_col);
+            ldmatrix_x4(a0, a1, a2, a3, as + a_row * TC_LD + kk + a_col);
 #pragma unroll
             for (int p = 0; p < 2; ++p) {          // two tiles of eight columns at a time
                 unsigned b0, b1, b2, b3;
-                ldmatrix_x4(b0, b1, b2, b3, Ws + (b_row + p * 16) * TC_LD + kk + b_col);
+                ldmatrix_x4(b0, b1, b2, b3, ws + (b_row + p * 16) * TC_LD + kk + b_col);
                 mma_bf16_16816(acc + (2 * p) * 4, a0, a1, a2, a3, b0, b1);
                 mma_bf16_16816(acc + (2 * p + 1) * 4, a0, a1, a2, a3, b2, b3);
                 if (GLU) {
-                    ldmatrix_x4(b0, b1, b2, b3, W2s + (b_row + p * 16) * TC_LD + kk + b_col);
+                    ldmatrix_x4(b0, b1, b2, b3, w2s + (b_row + p * 16) * TC_LD + kk + b_col);
                     mma_bf16_16816(acc2 + (2 * p) * 4, a0, a1, a2, a3, b0, b1);
                     mma_bf16_16816(acc2 + (2 * p + 1) * 4, a0, a1, a2, a3, b2, b3);
                 }
             }
         }
-        __syncthreads();
     }
+    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+    __syncthreads();        // a second product of the same block may stage at once
 }
 
 // C = A W^T for a float32 A and a bfloat16 W on the tensor cores without rounding A: every element of A is cut into two
@@ -558,30 +581,48 @@ __global__ void __launch_bounds__(LA_WARPS * 32) latent_attention_kernel(LatentA
     }
 }
 
-// one warp per (row, head): the ranges' sums brought to one maximum and added in the order of the ranges
+// one warp per (row, head): the ranges' sums brought to one maximum and added in the order of the ranges.  The ranges'
+// factors exp(m_s - M) / l are formed once (a lane a range) and kept in shared memory; the sums then need no branch.
+constexpr int LM_WARPS = 4, LM_MAX_SPLITS = 64;
+
 template <typename T>
 __global__ void latent_merge_kernel(const float *__restrict__ part, T *__restrict__ out, int rows_heads, int R, int splits) {
     pdl_trigger();
     pdl_wait();
-    const int lane = threadIdx.x & 31;
-    const int idx = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    __shared__ float factor[LM_WARPS][LM_MAX_SPLITS];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int idx = blockIdx.x * LM_WARPS + warp;
     if (idx >= rows_heads) return;
     const float *p = part + (size_t)idx * splits * (R + 2);
+    float ms[LM_MAX_SPLITS / 32], ls[LM_MAX_SPLITS / 32];
     float M = -INFINITY;
-    for (int s = 0; s < splits; ++s) M = fmaxf(M, p[(size_t)s * (R + 2) + R]);
-    float l = 0.f;
-    for (int s = 0; s < splits; ++s) {
-        const float ms = p[(size_t)s * (R + 2) + R];
-        if (ms > -INFINITY) l += p[(size_t)s * (R + 2) + R + 1] * expf(ms - M);
+#pragma unroll
+    for (int i = 0; i < LM_MAX_SPLITS / 32; ++i) {
+        const int s = lane + 32 * i;
+        ms[i] = s < splits ? p[(size_t)s * (R + 2) + R] : -INFINITY;
+        ls[i] = s < splits ? p[(size_t)s * (R + 2) + R + 1] : 0.f;
+        M = fmaxf(M, ms[i]);
     }
+    M = warp_max(M);
+    float l = 0.f;
+#pragma unroll
+    for (int i = 0; i < LM_MAX_SPLITS / 32; ++i) {
+        ms[i] = ms[i] > -INFINITY ? expf(ms[i] - M) : 0.f;
+        l += ls[i] * ms[i];
+    }
+    l = warp_sum(l);
     const float inv = 1.f / l;
+#pragma unroll
+    for (int i = 0; i < LM_MAX_SPLITS / 32; ++i) {
+        const int s = lane + 32 * i;
+        if (s < splits) factor[warp][s] = ms[i] * inv;
+    }
+    __syncwarp();
     for (int e = lane; e < R; e += 32) {
         float v = 0.f;
-        for (int s = 0; s < splits; ++s) {
-            const float ms = p[(size_t)s * (R + 2) + R];
-            if (ms > -INFINITY) v = fmaf(p[(size_t)s * (R + 2) + e], expf(ms - M), v);
-        }
-        out[(size_t)idx * R + e] = from_f32<T>(v * inv);
+#pragma unroll 4
+        for (int s = 0; s < splits; ++s) v = fmaf(p[(size_t)s * (R + 2) + e], factor[warp][s], v);
+        out[(size_t)idx * R + e] = from_f32<T>(v);
     }
 }
 
@@ -860,7 +901,7 @@ JK_EXPORT int jk_latent_attention(const void *q, const void *pages, void *out, f
     JK_REQUIRE(T <= 65535, "latent_attention: %d rows exceed one launch (65535)", T);
     if (splits < 1) splits = 1;
     JK_REQUIRE(splits == 1 || part != nullptr, "latent_attention: split keys need room for their parts");
-    JK_REQUIRE(splits <= 65535, "latent_attention: %d ranges", splits);
+    JK_REQUIRE(splits <= LM_MAX_SPLITS, "latent_attention: %d ranges exceed %d", splits, LM_MAX_SPLITS);
     const int D = R + dr;
     if (dtype == JK_BF16 && req_start != nullptr && nreq > 0 && R <= 512 && latent_tc_enabled()) {
         int HT = 1;
