@@ -53,7 +53,16 @@ __device__ __forceinline__ float block_act(int act, float z) {
 // out[r] = T(x[r] / sqrt(mean(x[r]^2) + eps2) * w_next)   (w_next null: out[r] = T(x[r])).
 // One block per row; the row stays in shared memory between the passes.
 // ---------------------------------------------------------------------------------------------------------------
-template <typename T>
+__device__ __forceinline__ void store4(float *p, float4 v) { *reinterpret_cast<float4 *>(p) = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16 *p, float4 v) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 raw;
+    raw.x = *reinterpret_cast<const unsigned *>(&lo); raw.y = *reinterpret_cast<const unsigned *>(&hi);
+    *reinterpret_cast<uint2 *>(p) = raw;
+}
+
+// VEC: the width is a multiple of four and every operand starts on a 16-byte boundary: four elements move at a time
+template <typename T, bool VEC>
 __global__ void norm_add_kernel(const float *__restrict__ delta, float *__restrict__ x, const float *__restrict__ w, float eps,
                                 const float *__restrict__ w_next, float eps2, T *__restrict__ out, int d) {
     pdl_trigger();
@@ -61,27 +70,47 @@ __global__ void norm_add_kernel(const float *__restrict__ delta, float *__restri
     extern __shared__ __align__(16) float row_buf[];
     __shared__ float scratch[33];
     const size_t base = (size_t)blockIdx.x * d;
+    constexpr int S = VEC ? 4 : 1;
     float ss = 0.f;
-    for (int c = threadIdx.x; c < d; c += blockDim.x) {
-        const float v = delta[base + c];
-        row_buf[c] = v;
-        ss += v * v;
+    for (int c = threadIdx.x * S; c < d; c += blockDim.x * S) {
+        if (VEC) {
+            const float4 v = *reinterpret_cast<const float4 *>(delta + base + c);
+            *reinterpret_cast<float4 *>(row_buf + c) = v;
+            ss += (v.x * v.x + v.y * v.y) + (v.z * v.z + v.w * v.w);
+        } else {
+            const float v = delta[base + c];
+            row_buf[c] = v;
+            ss += v * v;
+        }
     }
     const float inv = 1.f / sqrtf(block_sum(ss, scratch) / (float)d + eps);
     float ss2 = 0.f;
-    for (int c = threadIdx.x; c < d; c += blockDim.x) {
-        const float nx = x[base + c] + row_buf[c] * inv * w[c];
-        x[base + c] = nx;
-        row_buf[c] = nx;
-        ss2 += nx * nx;
+    for (int c = threadIdx.x * S; c < d; c += blockDim.x * S) {
+        if (VEC) {
+            const float4 xv = *reinterpret_cast<const float4 *>(x + base + c), wv = *reinterpret_cast<const float4 *>(w + c);
+            const float4 dv = *reinterpret_cast<const float4 *>(row_buf + c);
+            const float4 nx = make_float4(xv.x + dv.x * inv * wv.x, xv.y + dv.y * inv * wv.y, xv.z + dv.z * inv * wv.z, xv.w + dv.w * inv * wv.w);
+            *reinterpret_cast<float4 *>(x + base + c) = nx;
+            *reinterpret_cast<float4 *>(row_buf + c) = nx;
+            ss2 += (nx.x * nx.x + nx.y * nx.y) + (nx.z * nx.z + nx.w * nx.w);
+        } else {
+            const float nx = x[base + c] + row_buf[c] * inv * w[c];
+            x[base + c] = nx;
+            row_buf[c] = nx;
+            ss2 += nx * nx;
+        }
     }
     if (out == nullptr) return;
-    if (w_next == nullptr) {
-        for (int c = threadIdx.x; c < d; c += blockDim.x) out[base + c] = from_f32<T>(row_buf[c]);
-        return;
+    const float inv2 = w_next != nullptr ? 1.f / sqrtf(block_sum(ss2, scratch) / (float)d + eps2) : 1.f;
+    for (int c = threadIdx.x * S; c < d; c += blockDim.x * S) {
+        if (VEC) {
+            const float4 v = *reinterpret_cast<const float4 *>(row_buf + c);
+            const float4 wv = w_next != nullptr ? *reinterpret_cast<const float4 *>(w_next + c) : make_float4(1.f, 1.f, 1.f, 1.f);
+            store4(out + base + c, w_next != nullptr ? make_float4(v.x * inv2 * wv.x, v.y * inv2 * wv.y, v.z * inv2 * wv.z, v.w * inv2 * wv.w) : v);
+        } else {
+            out[base + c] = from_f32<T>(w_next != nullptr ? row_buf[c] * inv2 * w_next[c] : row_buf[c]);
+        }
     }
-    const float inv2 = 1.f / sqrtf(block_sum(ss2, scratch) / (float)d + eps2);
-    for (int c = threadIdx.x; c < d; c += blockDim.x) out[base + c] = from_f32<T>(row_buf[c] * inv2 * w_next[c]);
 }
 
 JK_EXPORT int jk_norm_add(const float *delta, float *x, const float *w, float eps, const float *w_next, float eps2, void *out,
@@ -90,12 +119,20 @@ JK_EXPORT int jk_norm_add(const float *delta, float *x, const float *w, float ep
     JK_REQUIRE(delta && x && w && rows > 0 && d > 0, "norm_add: rows %d, width %d", rows, d);
     const size_t smem = (size_t)d * sizeof(float);
     JK_REQUIRE(smem <= 200 * 1024, "norm_add: width %d does not fit shared memory", d);
-    const int threads = d >= 4096 ? 512 : (d >= 1024 ? 256 : 128);
-#define LAUNCH(T)                                                                                                              \
-    if (smem > 48 * 1024) cudaFuncSetAttribute(norm_add_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
-    jk_launch(norm_add_kernel<T>, dim3(rows), dim3(threads), smem, stream, delta, x, w, eps, w_next, eps2, (T *)out, d)
+    const bool vec = d % 4 == 0 && (uintptr_t)delta % 16 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)w % 16 == 0 &&
+                     (w_next == nullptr || (uintptr_t)w_next % 16 == 0) && (out == nullptr || (uintptr_t)out % 16 == 0);
+    // a step of few rows has few blocks: then a thread takes one vector of the row, so that a pass is one round of loads
+    int threads = d >= 4096 ? 512 : (d >= 1024 ? 256 : 128);
+    if (rows <= 64 && vec) threads = std::min(1024, std::max(threads, (d / 4 + 31) / 32 * 32));
+#define LAUNCH_V(T, V)                                                                                                              \
+    do {                                                                                                                            \
+        if (smem > 48 * 1024) cudaFuncSetAttribute(norm_add_kernel<T, V>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        jk_launch(norm_add_kernel<T, V>, dim3(rows), dim3(threads), smem, stream, delta, x, w, eps, w_next, eps2, (T *)out, d);   \
+    } while (0)
+#define LAUNCH(T) if (vec) LAUNCH_V(T, true); else LAUNCH_V(T, false)
     BLOCKS_BY_DTYPE(dtype, "norm_add", LAUNCH);
 #undef LAUNCH
+#undef LAUNCH_V
     JK_CHECK_LAUNCH("norm_add");
     return JK_OK;
 }
@@ -581,47 +618,55 @@ __global__ void __launch_bounds__(LA_WARPS * 32) latent_attention_kernel(LatentA
     }
 }
 
-// one warp per (row, head): the ranges' sums brought to one maximum and added in the order of the ranges.  The ranges'
-// factors exp(m_s - M) / l are formed once (a lane a range) and kept in shared memory; the sums then need no branch.
-constexpr int LM_WARPS = 4, LM_MAX_SPLITS = 64;
+// one block per (row, head): the ranges' sums brought to one maximum and added in the order of the ranges.  The ranges'
+// factors exp(m_s - M) / l are formed once by the first warp (a lane a range) and kept in shared memory; a thread then
+// takes columns, with all ranges' loads of a column asked for before the sum starts.
+constexpr int LM_THREADS = 128, LM_MAX_SPLITS = 64;
 
 template <typename T>
-__global__ void latent_merge_kernel(const float *__restrict__ part, T *__restrict__ out, int rows_heads, int R, int splits) {
+__global__ void __launch_bounds__(LM_THREADS) latent_merge_kernel(const float *__restrict__ part, T *__restrict__ out, int rows_heads, int R, int splits) {
     pdl_trigger();
     pdl_wait();
-    __shared__ float factor[LM_WARPS][LM_MAX_SPLITS];
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int idx = blockIdx.x * LM_WARPS + warp;
-    if (idx >= rows_heads) return;
+    __shared__ float factor[LM_MAX_SPLITS];
+    const int lane = threadIdx.x & 31, idx = blockIdx.x;
     const float *p = part + (size_t)idx * splits * (R + 2);
-    float ms[LM_MAX_SPLITS / 32], ls[LM_MAX_SPLITS / 32];
-    float M = -INFINITY;
+    if (threadIdx.x < 32) {
+        float ms[LM_MAX_SPLITS / 32], ls[LM_MAX_SPLITS / 32];
+        float M = -INFINITY;
 #pragma unroll
-    for (int i = 0; i < LM_MAX_SPLITS / 32; ++i) {
-        const int s = lane + 32 * i;
-        ms[i] = s < splits ? p[(size_t)s * (R + 2) + R] : -INFINITY;
-        ls[i] = s < splits ? p[(size_t)s * (R + 2) + R + 1] : 0.f;
-        M = fmaxf(M, ms[i]);
-    }
-    M = warp_max(M);
-    float l = 0.f;
+        for (int i = 0; i < LM_MAX_SPLITS / 32; ++i) {
+            const int s = lane + 32 * i;
+            ms[i] = s < splits ? p[(size_t)s * (R + 2) + R] : -INFINITY;
+            ls[i] = s < splits ? p[(size_t)s * (R + 2) + R + 1] : 0.f;
+            M = fmaxf(M, ms[i]);
+        }
+        M = warp_max(M);
+        float l = 0.f;
 #pragma unroll
-    for (int i = 0; i < LM_MAX_SPLITS / 32; ++i) {
-        ms[i] = ms[i] > -INFINITY ? expf(ms[i] - M) : 0.f;
-        l += ls[i] * ms[i];
-    }
-    l = warp_sum(l);
-    const float inv = 1.f / l;
+        for (int i = 0; i < LM_MAX_SPLITS / 32; ++i) {
+            ms[i] = ms[i] > -INFINITY ? expf(ms[i] - M) : 0.f;
+            l += ls[i] * ms[i];
+        }
+        l = warp_sum(l);
+        const float inv = 1.f / l;
 #pragma unroll
-    for (int i = 0; i < LM_MAX_SPLITS / 32; ++i) {
-        const int s = lane + 32 * i;
-        if (s < splits) factor[warp][s] = ms[i] * inv;
+        for (int i = 0; i < LM_MAX_SPLITS / 32; ++i) {
+            const int s = lane + 32 * i;
+            if (s < splits) factor[s] = ms[i] * inv;
+        }
     }
-    __syncwarp();
-    for (int e = lane; e < R; e += 32) {
+    __syncthreads();
+    for (int e = threadIdx.x; e < R; e += LM_THREADS) {
         float v = 0.f;
-#pragma unroll 4
-        for (int s = 0; s < splits; ++s) v = fmaf(p[(size_t)s * (R + 2) + e], factor[warp][s], v);
+        int s = 0;
+        for (; s + 8 <= splits; s += 8) {
+            float t[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) t[i] = p[(size_t)(s + i) * (R + 2) + e];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v = fmaf(t[i], factor[s + i], v);
+        }
+        for (; s < splits; ++s) v = fmaf(p[(size_t)s * (R + 2) + e], factor[s], v);
         out[(size_t)idx * R + e] = from_f32<T>(v);
     }
 }
@@ -909,13 +954,16 @@ JK_EXPORT int jk_latent_attention(const void *q, const void *pages, void *out, f
         const int RT = LT_PAIRS / HT, tiles8 = (R + 7) / 8, per = (tiles8 + 3) / 4;
         const int NT = per <= 2 ? 2 : (per <= 4 ? 4 : (per <= 8 ? 8 : 16));
         const int DP = (D + 15) / 16 * 16, ldk = std::max(DP, 4 * NT * 8) + 8;
-        // two tile buffers unless that leaves an SM (about 227 KB, 1 KB a block reserved) room for one block where one buffer leaves room for two
+        // two tile buffers unless that leaves an SM (about 227 KB, 1 KB a block reserved) room for one block where one buffer leaves
+        // room for two and the launch has more blocks than SMs
         const size_t fixed = (size_t)LT_PAIRS * (DP + 8) * 2 + 2 * 16 * 33 * sizeof(float), tile = (size_t)LT_KEYS * ldk * 2;
-        const int buffers = (fixed + 2 * tile > 112 * 1024 && fixed + tile <= 112 * 1024) ? 1 : 2;
+        dim3 grid((T + RT - 1) / RT + nreq, (H + HT - 1) / HT, splits);
+        static const int sms = [] { int n = 148, dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev); return n; }();
+        const bool second_block_fits = fixed + 2 * tile > 112 * 1024 && fixed + tile <= 112 * 1024;
+        const int buffers = (second_block_fits && (long long)((T + RT - 1) / RT) * grid.y * grid.z > sms) ? 1 : 2;
         LatentTcArgs ta{(const __nv_bfloat16 *)q, (const __nv_bfloat16 *)pages, (__nv_bfloat16 *)out, part, positions, req_start, block_table,
                         nreq, H, R, dr, page_size, max_blocks, splits, HT, RT, ldk, scale, buffers};
         const size_t smem_tc = fixed + buffers * tile;
-        dim3 grid((T + RT - 1) / RT + nreq, (H + HT - 1) / HT, splits);
         JK_REQUIRE(grid.y <= 65535, "latent_attention: %d heads", H);
 #define LAUNCH_TC(NT_)                                                                                                                       \
     do {                                                                                                                                    \
@@ -927,7 +975,7 @@ JK_EXPORT int jk_latent_attention(const void *q, const void *pages, void *out, f
         JK_CHECK_LAUNCH("latent_attention_tc");
         if (splits > 1) {
             const int n = T * H;
-            jk_launch(latent_merge_kernel<__nv_bfloat16>, dim3((n + 3) / 4), dim3(128), 0, stream, (const float *)part, (__nv_bfloat16 *)out, n, R, splits);
+            jk_launch(latent_merge_kernel<__nv_bfloat16>, dim3(n), dim3(LM_THREADS), 0, stream, (const float *)part, (__nv_bfloat16 *)out, n, R, splits);
             JK_CHECK_LAUNCH("latent_merge");
         }
         return JK_OK;
@@ -953,7 +1001,7 @@ JK_EXPORT int jk_latent_attention(const void *q, const void *pages, void *out, f
     JK_CHECK_LAUNCH("latent_attention");
     if (splits > 1) {
         const int n = T * H;
-#define LAUNCH(TT) jk_launch(latent_merge_kernel<TT>, dim3((n + 3) / 4), dim3(128), 0, stream, (const float *)part, (TT *)out, n, R, splits)
+#define LAUNCH(TT) jk_launch(latent_merge_kernel<TT>, dim3(n), dim3(LM_THREADS), 0, stream, (const float *)part, (TT *)out, n, R, splits)
         BLOCKS_BY_DTYPE(dtype, "latent_merge", LAUNCH);
 #undef LAUNCH
         JK_CHECK_LAUNCH("latent_merge");
@@ -1235,10 +1283,23 @@ __global__ void route_topk_kernel(const T *__restrict__ h, const float *__restri
     extern __shared__ float z[];        // [E]
     const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
     const T *row = h + (size_t)t * D;
+    const bool vec = D % 8 == 0 && (uintptr_t)row % 16 == 0 && (uintptr_t)router % 16 == 0;
     for (int e = warp; e < E; e += nwarp) {
         const float *w = router + (size_t)e * D;
         float dot = 0.f;
-        for (int c = lane; c < D; c += 32) dot = fmaf(w[c], to_f32(row[c]), dot);
+        if (vec) {          // eight elements a lane a pass, the passes' loads independent of one another
+#pragma unroll 4
+            for (int c = lane * 8; c < D; c += 256) {
+                const float4 w0 = *reinterpret_cast<const float4 *>(w + c), w1 = *reinterpret_cast<const float4 *>(w + c + 4);
+                float x[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) x[i] = to_f32(row[c + i]);
+                dot = fmaf(w0.x, x[0], dot); dot = fmaf(w0.y, x[1], dot); dot = fmaf(w0.z, x[2], dot); dot = fmaf(w0.w, x[3], dot);
+                dot = fmaf(w1.x, x[4], dot); dot = fmaf(w1.y, x[5], dot); dot = fmaf(w1.z, x[6], dot); dot = fmaf(w1.w, x[7], dot);
+            }
+        } else {
+            for (int c = lane; c < D; c += 32) dot = fmaf(w[c], to_f32(row[c]), dot);
+        }
         dot = warp_sum(dot);
         if (lane == 0) z[e] = dot;
     }
@@ -1273,17 +1334,26 @@ __global__ void route_sort_kernel(const int *__restrict__ ids, const float *__re
         if (e == E - 1) starts[E] = start + counts[e];
     }
     int at = start;
-    for (int p0 = 0; p0 < pairs; p0 += 32) {
-        const int p = p0 + lane;
-        const bool mine = p < pairs && ids[p] == e;
-        const unsigned ballot = __ballot_sync(0xffffffffu, mine);
-        if (mine) {
-            const int pos = at + __popc(ballot & ((1u << lane) - 1u));
-            entry_row[pos] = p / top;
-            entry_score[pos] = scores[p];
-            pair_entry[p] = pos;
+    for (int p0 = 0; p0 < pairs; p0 += 128) {          // four passes of 32 pairs, their loads asked for together
+        int id[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int p = p0 + 32 * i + lane;
+            id[i] = p < pairs ? ids[p] : -1;
         }
-        at += __popc(ballot);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int p = p0 + 32 * i + lane;
+            const bool mine = id[i] == e;
+            const unsigned ballot = __ballot_sync(0xffffffffu, mine);
+            if (mine) {
+                const int pos = at + __popc(ballot & ((1u << lane) - 1u));
+                entry_row[pos] = p / top;
+                entry_score[pos] = scores[p];
+                pair_entry[p] = pos;
+            }
+            at += __popc(ballot);
+        }
     }
 }
 
@@ -1345,6 +1415,110 @@ __global__ void __launch_bounds__(256) expert_down_kernel(const T *__restrict__ 
     }
 }
 
+// Steps of few rows (decoding): an expert has a handful of entries, and its matrices only have to stream past them.  A
+// block of eight warps takes one expert and a slice of its output features; the expert's entries (up to ER_ROWS at a
+// time) wait in shared memory; a warp takes one feature at a time, its lanes 16 bytes of the weight row each
+// per pass, all loads of a row asked for before the sums start.  Float32 sums on the CUDA cores, in the order of K per
+// lane and then across lanes, whatever else the step holds.
+constexpr int ER_ROWS = 8, ER_FEATURES = 32;        // entries at a time; output features a block
+
+template <typename T> struct Vec16;
+template <> struct Vec16<float> { static constexpr int N = 4; };
+template <> struct Vec16<__nv_bfloat16> { static constexpr int N = 8; };
+
+template <typename T>
+__device__ __forceinline__ void unpack16(const uint4 &v, float *f) {
+    if constexpr (Vec16<T>::N == 4) {
+        f[0] = __uint_as_float(v.x); f[1] = __uint_as_float(v.y); f[2] = __uint_as_float(v.z); f[3] = __uint_as_float(v.w);
+    } else {
+        const unsigned w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { f[2 * i] = __uint_as_float(w[i] << 16); f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u); }
+    }
+}
+
+// the features of one block against ROWS staged entries (the caller picks the smallest ROWS that holds them)
+template <typename T, bool GLU, int ROWS>
+__device__ __forceinline__ void expert_rows_features(const T *__restrict__ er_rows, const T *__restrict__ we, void *__restrict__ out, int K, int N,
+                                                     int rows, size_t entry0, const float *__restrict__ entry_score, int actf) {
+    constexpr int V = Vec16<T>::N;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int f = warp; f < ER_FEATURES; f += 8) {
+        const int n = blockIdx.y * ER_FEATURES + f;
+        if (n >= N) break;
+        const T *wg = we + (size_t)n * K, *wu = we + (size_t)(N + n) * K;
+        float g[ROWS], u[ROWS];
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) { g[r] = 0.f; u[r] = 0.f; }
+#pragma unroll 4
+        for (int k = lane * V; k < K; k += 32 * V) {
+            float a[V], b[V];
+            unpack16<T>(*reinterpret_cast<const uint4 *>(wg + k), a);
+            if (GLU) unpack16<T>(*reinterpret_cast<const uint4 *>(wu + k), b);
+#pragma unroll
+            for (int r = 0; r < ROWS; ++r) {
+                float x[V];
+                unpack16<T>(*reinterpret_cast<const uint4 *>(er_rows + r * K + k), x);
+#pragma unroll
+                for (int i = 0; i < V; ++i) {
+                    g[r] = fmaf(a[i], x[i], g[r]);
+                    if (GLU) u[r] = fmaf(b[i], x[i], u[r]);
+                }
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) {
+            g[r] = warp_sum(g[r]);
+            if (GLU) u[r] = warp_sum(u[r]);
+        }
+        if (lane == 0) {
+#pragma unroll
+            for (int r = 0; r < ROWS; ++r) {
+                if (r >= rows) break;
+                const size_t entry = entry0 + r;
+                if (GLU) {
+                    const float sc = entry_score[entry];
+                    ((T *)out)[entry * N + n] = from_f32<T>(block_act(actf, sc * g[r]) * (sc * u[r]));
+                } else {
+                    ((float *)out)[entry * N + n] = g[r];
+                }
+            }
+        }
+    }
+}
+
+// GLU: act[entry, n] = T(actf(s g) (s u)) from rows of h picked by entry_row; else y[entry, n] = W[e][n] . in[entry]
+template <typename T, bool GLU>
+__global__ void __launch_bounds__(256) expert_rows_kernel(const T *__restrict__ in, const T *__restrict__ w, void *__restrict__ out, int K, int N, int E,
+                                                          const int *__restrict__ starts, const int *__restrict__ entry_row,
+                                                          const float *__restrict__ entry_score, int actf) {
+    pdl_trigger();
+    pdl_wait();
+    extern __shared__ __align__(16) unsigned char er_smem[];
+    T *er_rows = reinterpret_cast<T *>(er_smem);             // [ER_ROWS][K] as they are stored
+    const int e = blockIdx.x, first = starts[e], M = starts[e + 1] - first;
+    if (M <= 0) return;
+    constexpr int V = Vec16<T>::N;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const T *we = w + (size_t)e * (GLU ? 2 : 1) * N * K;
+    for (int r0 = 0; r0 < M; r0 += ER_ROWS) {
+        const int rows = min(ER_ROWS, M - r0);
+        __syncthreads();
+        if (warp < rows) {      // warp r brings entry r: one look at where it lies, then 16 bytes a lane a pass
+            const T *src = in + (size_t)(GLU ? entry_row[first + r0 + warp] : first + r0 + warp) * K;
+#pragma unroll 4
+            for (int k = lane * V; k < K; k += 32 * V)
+                *reinterpret_cast<uint4 *>(er_rows + warp * K + k) = *reinterpret_cast<const uint4 *>(src + k);
+        }
+        __syncthreads();
+        const size_t entry0 = (size_t)(first + r0);
+        if (rows <= 1) expert_rows_features<T, GLU, 1>(er_rows, we, out, K, N, rows, entry0, entry_score, actf);
+        else if (rows <= 2) expert_rows_features<T, GLU, 2>(er_rows, we, out, K, N, rows, entry0, entry_score, actf);
+        else if (rows <= 4) expert_rows_features<T, GLU, 4>(er_rows, we, out, K, N, rows, entry0, entry_score, actf);
+        else expert_rows_features<T, GLU, 8>(er_rows, we, out, K, N, rows, entry0, entry_score, actf);
+    }
+}
+
 // delta[t] (+)= sum over the row's choices, in their order, of y[pair_entry[t * top + k]]
 __global__ void expert_combine_kernel(const float *__restrict__ y, const int *__restrict__ pair_entry, float *__restrict__ delta, int D, int top,
                                       int add, size_t total) {
@@ -1383,6 +1557,23 @@ JK_EXPORT int jk_routed_experts(const void *h, const float *router, const void *
     jk_launch(route_sort_kernel, dim3((E + 3) / 4), dim3(128), 0, stream, (const int *)ids, (const float *)scores, (const int *)counts, pairs, E, top,
               starts, entry_row, entry_score, pair_entry);
     JK_CHECK_LAUNCH("route_sort");
+    // few rows: the experts' matrices stream past their entries (rows of 16-byte multiples); else tiles
+    const int per16 = dtype == JK_F32 ? 4 : 8;
+    const bool stream_rows = pairs <= 64 && D % per16 == 0 && ff % per16 == 0 && (uintptr_t)w_gate_up % 16 == 0 && (uintptr_t)w_down % 16 == 0 &&
+                             (size_t)ER_ROWS * std::max(D, ff) * 4 <= 160 * 1024;
+    if (stream_rows) {
+        const size_t elem = dtype == JK_F32 ? 4 : 2, smem_up = (size_t)ER_ROWS * D * elem, smem_down = (size_t)ER_ROWS * ff * elem;
+#define LAUNCH(TT)                                                                                                                           \
+    if (smem_up > 48 * 1024) cudaFuncSetAttribute(expert_rows_kernel<TT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_up);  \
+    if (smem_down > 48 * 1024) cudaFuncSetAttribute(expert_rows_kernel<TT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_down); \
+    jk_launch(expert_rows_kernel<TT, true>, dim3(E, (ff + ER_FEATURES - 1) / ER_FEATURES), dim3(256), smem_up, stream, (const TT *)h,        \
+              (const TT *)w_gate_up, act, D, ff, E, (const int *)starts, (const int *)entry_row, (const float *)entry_score, actf);          \
+    jk_launch(expert_rows_kernel<TT, false>, dim3(E, (D + ER_FEATURES - 1) / ER_FEATURES), dim3(256), smem_down, stream, (const TT *)act,    \
+              (const TT *)w_down, (void *)y, ff, D, E, (const int *)starts, (const int *)nullptr, (const float *)nullptr, 0)
+        BLOCKS_BY_DTYPE(dtype, "expert rows", LAUNCH);
+#undef LAUNCH
+        JK_CHECK_LAUNCH("expert rows");
+    } else {
     const int tiles = (pairs + GT_M - 1) / GT_M + E;
 #define LAUNCH(TT)                                                                                                                          \
     jk_launch(expert_gate_up_kernel<TT>, dim3(tiles, (ff + GT_N - 1) / GT_N), dim3(256), 0, stream, (const TT *)h, (const TT *)w_gate_up,  \
@@ -1392,6 +1583,7 @@ JK_EXPORT int jk_routed_experts(const void *h, const float *router, const void *
     BLOCKS_BY_DTYPE(dtype, "expert products", LAUNCH);
 #undef LAUNCH
     JK_CHECK_LAUNCH("expert products");
+    }
     const size_t total = (size_t)T * D;
     jk_launch(expert_combine_kernel, dim3((int)std::min<size_t>((total + 255) / 256, 148 * 16)), dim3(256), 0, stream, (const float *)y,
               (const int *)pair_entry, delta, D, top, add, total);
