@@ -1162,8 +1162,11 @@ __global__ void __launch_bounds__(SS_THREADS) selective_scan_kernel(ScanArgs a) 
     }
     for (int t0 = first; t0 < last; t0 += SS_CHUNK) {
         const int n_rows = min(SS_CHUNK, last - t0);
-        for (int idx = threadIdx.x; idx < n_rows * SS_CHANNELS; idx += SS_THREADS) {
+        // the loops below are unrolled so that a thread's loads are asked for together, not one after the other's arrival
+#pragma unroll 4
+        for (int idx = threadIdx.x; idx < SS_CHUNK * SS_CHANNELS; idx += SS_THREADS) {
             const int tt = idx / SS_CHANNELS, ch = min(c0 + idx % SS_CHANNELS, a.E - 1);
+            if (tt >= n_rows) { s_dt[idx] = 0.f; s_x[idx] = 0.f; continue; }
             const size_t t = (size_t)(t0 + tt);
             float dt;
             if (a.dt != nullptr) {
@@ -1178,30 +1181,49 @@ __global__ void __launch_bounds__(SS_THREADS) selective_scan_kernel(ScanArgs a) 
             s_dt[idx] = dt;
             s_x[idx] = a.x[t * a.E + ch];
         }
-        for (int idx = threadIdx.x; idx < n_rows * a.N; idx += SS_THREADS) {
+#pragma unroll 4
+        for (int idx = threadIdx.x; idx < SS_CHUNK * a.N; idx += SS_THREADS) {
             const int tt = idx / a.N, n = idx % a.N;
-            const float *low = a.low + (size_t)(t0 + tt) * a.ld_low + a.K;
+            const float *low = a.low + (size_t)(t0 + min(tt, n_rows - 1)) * a.ld_low + a.K;
             s_B[idx] = low[n];
             s_C[idx] = low[a.N + n];
         }
         __syncthreads();
-#pragma unroll 4
-        for (int tt = 0; tt < n_rows; ++tt) {
-            const float dt = s_dt[tt * SS_CHANNELS + cl], xv = s_x[tt * SS_CHANNELS + cl];
-            const float dx = dt * xv;
-            const float *Bt = s_B + tt * a.N, *Ct = s_C + tt * a.N;
-            float y = 0.f;
+        // four rows at a time: their step sizes, inputs, B and C into registers first, then the four updates in order, then
+        // the four shares; rows beyond the chunk's end were staged as dt = 0, x = 0 and leave the state as it is
+        for (int t4 = 0; t4 < n_rows; t4 += 4) {
+            float dt4[4], dx4[4], B4[4][NPER], C4[4][NPER], y4[4];
 #pragma unroll
-            for (int i = 0; i < NPER; ++i) {
-                const int n = part + SS_LANES * i;
-                if (n < a.N) {
-                    s[i] = fmaf(expf(dt * An[i]), s[i], dx * Bt[n]);
-                    y = fmaf(s[i], Ct[n], y);
+            for (int j = 0; j < 4; ++j) {
+                dt4[j] = s_dt[(t4 + j) * SS_CHANNELS + cl];
+                dx4[j] = dt4[j] * s_x[(t4 + j) * SS_CHANNELS + cl];
+#pragma unroll
+                for (int i = 0; i < NPER; ++i) {
+                    const int n = part + SS_LANES * i;
+                    B4[j][i] = n < a.N ? s_B[(t4 + j) * a.N + n] : 0.f;
+                    C4[j][i] = n < a.N ? s_C[(t4 + j) * a.N + n] : 0.f;
                 }
             }
-            s_y[tt * SS_THREADS + threadIdx.x] = y;
+            float decay[4][NPER];
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+#pragma unroll
+                for (int i = 0; i < NPER; ++i) decay[j][i] = expf(dt4[j] * An[i]);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                float y = 0.f;
+#pragma unroll
+                for (int i = 0; i < NPER; ++i) {
+                    s[i] = fmaf(decay[j][i], s[i], dx4[j] * B4[j][i]);
+                    y = fmaf(s[i], C4[j][i], y);
+                }
+                y4[j] = y;
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) s_y[(t4 + j) * SS_THREADS + threadIdx.x] = y4[j];
         }
         __syncthreads();
+#pragma unroll 4
         for (int idx = threadIdx.x; idx < n_rows * SS_CHANNELS; idx += SS_THREADS) {
             const int tt = idx / SS_CHANNELS, k = idx % SS_CHANNELS, ch = c0 + k;
             if (ch < a.E) {
