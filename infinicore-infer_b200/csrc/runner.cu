@@ -343,8 +343,8 @@ int run_gate_up(Run &r, const RunnerOp &op, const FusedNorm &fused) {
     // the gate's activation rides above the epilogue's code (common.cuh: gated_unit)
     JK_REQUIRE(op.act == RUNNER_ACT_NONE || op.act == RUNNER_ACT_SILU || op.act == RUNNER_ACT_GELU_TANH || op.act == RUNNER_ACT_RELU,
                "runner: a gated unit with activation %d is not built", op.act);
-    const bool gelu = op.act == RUNNER_ACT_GELU_TANH || op.act == RUNNER_ACT_RELU;      // not silu: the unfused unit is the mixers module's
-    const int gate_bits = gelu ? (op.act << 8) : 0;
+    const bool other_gate = op.act == RUNNER_ACT_GELU_TANH || op.act == RUNNER_ACT_RELU;      // not silu: the unfused unit is the mixers module's
+    const int gate_bits = other_gate ? (op.act << 8) : 0;
     if (fused.norm != nullptr) {
         RUN(linear_small, g_fns.linear_small_norm(h, op.w, act, T, di, d, di, 1 | gate_bits, fused.sumsq, fused.norm->eps, nullptr, nullptr, nullptr,
                                                   1.f, r.env.status, ro.sms, r.stream));
@@ -372,7 +372,7 @@ int run_gate_up(Run &r, const RunnerOp &op, const FusedNorm &fused) {
     } else {
         if (int rc = lt_product(h, op.w, (float *)tmp, T, 2 * di, d, r.buf, r.stream)) return rc;
     }
-    if (gelu) {
+    if (other_gate) {
         JK_REQUIRE(g_fns.glu != nullptr, "runner: the unfused gated unit with activation %d needs the mixers module", op.act);
         RUN(mixers, g_fns.glu((const float *)tmp, act, r.env.dtype, T, di, op.act, r.stream));
         return JK_OK;
